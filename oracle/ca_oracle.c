@@ -1,0 +1,458 @@
+/*
+ * CPU oracle of the multi-head Flow-Lenia neural-CA step and of its fitness reduction.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA path is compared with; nothing in the
+ * product library calls, links or loads it.  It is compiled twice by the Makefile beside it:
+ *   libca_oracle_f64.so  (-DORACLE_REAL=double)  every intermediate in fp64: the truth used by tests;
+ *   libca_oracle_f32.so  (-DORACLE_REAL=float)   fp32 intermediates, fp64 reductions: the timed CPU
+ *                                                transcription of the step (multithreaded, OpenMP).
+ *
+ * PARITY UNPINNED BY THE REFERENCE: J0pari/Slime ships no golden vector, known-answer test or fixture
+ * for this path, has no CPU implementation, and its live CUDA step is racy and mis-indexed
+ * (slime/core/organism.cu:617-688 launches the child sequence from 128 threads at once;
+ * slime/core/pseudopod.cu:54 visits only the diagonal tiles), so it cannot produce reference outputs.
+ * The oracle is pinned instead against an independently written numpy restatement
+ * (tests/golden/make_golden.py) and against the invariants the reference's own documents state
+ * (per-channel mass, buildplan.md:179; rank range, effective_rank tests recorded in .test_checkpoints).
+ *
+ * The step, stage by stage, with the reference lines each stage follows (paths inside J0pari/Slime):
+ *   1 projections   P_h = X Wp_h, I_h = X Wi_h, V_h = X Wv_h   weight order [head][c_in][d_out]
+ *                   slime/core/pseudopod.cu:78-120 (index order :86-87), buildplan.md:572-592
+ *   2 stencil       U_h(y,x,d) = sum_t K_h[t] P_h(y+dy,x+dx,d), t=(dy+1)*3+(dx+1), torus
+ *                   slime/core/pseudopod.cu:153,172-180 (tap order), slime/kernels/warp_ca.cu:305-306 (wrap)
+ *   3 growth        G = 2 exp(-(U-mu)^2 / (2 sigma^2)) - 1
+ *                   failed_attempts/warp_ca.cu:49-56, failed_attempts/pseudopod.cu:46-48
+ *   4 activation    A = G * I                                  README.md:42-45
+ *   5 flow weights  source s sends to n in N(s) the share softmax_n(A(n)), max-subtracted
+ *                   failed_attempts/pseudopod.cu:234-251, buildplan.md:608-622
+ *   6 propagation   V'(n) = sum_{s in N(n)} w(s->n) V(s)        README.md:45-47 (sum out = sum in)
+ *   7 output proj   Y = concat_h(V'_h) Wo                      slime/core/pseudopod.cu:217-253
+ *   8 residual      X+ = X + dt Y, dt = 0.1                    slime/core/pseudopod.cu:186-187, organism.cu:659
+ *   9 renorm        X+[:,:,c] *= M_c / sum_cells X+[:,:,c]     failed_attempts/warp_ca.cu:401-450
+ * Fitness: Gram of each head's V' (64x64 over cells), cyclic two-sided Jacobi, exp-entropy rank, Pearson
+ * coherence of V' between the last two steps, fitness = rank x coherence, hunger = 1 - coherence
+ *   failed_attempts/pseudopod.cu:366-432, slime/kernels/warp_ca.cu:51-63,107-144,219,238.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#ifndef ORACLE_REAL
+#define ORACLE_REAL double
+#endif
+typedef ORACLE_REAL real;
+
+#define NH 8   /* heads            slime/core/pseudopod.cu:15 */
+#define HD 64  /* head dim         slime/core/pseudopod.cu:16 */
+#define NC 64  /* state channels                              */
+#define HC (NH * HD)
+
+static inline real r_exp(real x) { return sizeof(real) == 4 ? (real)expf((float)x) : (real)exp((double)x); }
+
+static inline int wrap(int i, int n) { i %= n; return i < 0 ? i + n : i; }
+
+/* One weight set, host fp32, in the reference's index order. */
+typedef struct {
+    const float* Wp;    /* [8][64][64]  [head][c_in][d_out] */
+    const float* Wi;    /* [8][64][64] */
+    const float* Wv;    /* [8][64][64] */
+    const float* Wo;    /* [512][64]    [head*64+d][c_out]  */
+    const float* K;     /* [8][9]       taps t=(dy+1)*3+(dx+1), already softmax-normalised */
+    const float* mu;    /* [8] */
+    const float* sigma; /* [8] */
+} weight_set;
+
+int oracle_real_bytes(void) { return (int)sizeof(real); }
+
+/* ---- stage 1: projections for one head over one grid (cells x 64 -> cells x 64, three times) ---- */
+static void project_head(const float* X, int cells, const weight_set* w, int h, real* P, real* I, real* V) {
+    const float* wp = w->Wp + (size_t)h * NC * HD;
+    const float* wi = w->Wi + (size_t)h * NC * HD;
+    const float* wv = w->Wv + (size_t)h * NC * HD;
+#pragma omp parallel for schedule(static)
+    for (int s = 0; s < cells; ++s) {
+        real ap[HD], ai[HD], av[HD];
+        for (int d = 0; d < HD; ++d) ap[d] = ai[d] = av[d] = 0;
+        const float* x = X + (size_t)s * NC;
+        for (int c = 0; c < NC; ++c) {
+            real xc = (real)x[c];
+            const float* rp = wp + c * HD;
+            const float* ri = wi + c * HD;
+            const float* rv = wv + c * HD;
+            for (int d = 0; d < HD; ++d) {
+                ap[d] += xc * (real)rp[d];
+                ai[d] += xc * (real)ri[d];
+                av[d] += xc * (real)rv[d];
+            }
+        }
+        memcpy(P + (size_t)s * HD, ap, sizeof ap);
+        memcpy(I + (size_t)s * HD, ai, sizeof ai);
+        memcpy(V + (size_t)s * HD, av, sizeof av);
+    }
+}
+
+/* ---- stages 2-4: stencil on P, growth, activation; result A (overwrites nothing it reads) ---- */
+static void activation_head(const real* P, const real* I, int H, int W, const weight_set* w, int h, real* A) {
+    const float* k = w->K + h * 9;
+    const real mu = (real)w->mu[h];
+    const real sg = (real)w->sigma[h];
+    const real inv2s2 = (real)1 / ((real)2 * sg * sg);
+#pragma omp parallel for schedule(static)
+    for (int y = 0; y < H; ++y) {
+        for (int x = 0; x < W; ++x) {
+            real u[HD];
+            for (int d = 0; d < HD; ++d) u[d] = 0;
+            for (int dy = -1; dy <= 1; ++dy)
+                for (int dx = -1; dx <= 1; ++dx) {
+                    const real kt = (real)k[(dy + 1) * 3 + (dx + 1)];
+                    const real* p = P + ((size_t)wrap(y + dy, H) * W + wrap(x + dx, W)) * HD;
+                    for (int d = 0; d < HD; ++d) u[d] += kt * p[d];
+                }
+            const size_t o = ((size_t)y * W + x) * HD;
+            for (int d = 0; d < HD; ++d) {
+                const real z = u[d] - mu;
+                const real g = (real)2 * r_exp(-(z * z) * inv2s2) - (real)1;
+                A[o + d] = g * I[o + d];
+            }
+        }
+    }
+}
+
+/* ---- stages 5-6, literal form: per-source max-subtracted softmax over its 3x3 targets, then gather ---- */
+static void redistribute_literal(const real* A, const real* V, int H, int W, real* mx, real* den, real* Vp) {
+#pragma omp parallel for schedule(static)
+    for (int y = 0; y < H; ++y)
+        for (int x = 0; x < W; ++x) {
+            const size_t o = ((size_t)y * W + x) * HD;
+            for (int d = 0; d < HD; ++d) {
+                real m = -INFINITY;
+                for (int dy = -1; dy <= 1; ++dy)
+                    for (int dx = -1; dx <= 1; ++dx) {
+                        const real a = A[((size_t)wrap(y + dy, H) * W + wrap(x + dx, W)) * HD + d];
+                        if (a > m) m = a;
+                    }
+                real sden = 0;
+                for (int dy = -1; dy <= 1; ++dy)
+                    for (int dx = -1; dx <= 1; ++dx)
+                        sden += r_exp(A[((size_t)wrap(y + dy, H) * W + wrap(x + dx, W)) * HD + d] - m);
+                mx[o + d] = m;
+                den[o + d] = sden;
+            }
+        }
+#pragma omp parallel for schedule(static)
+    for (int y = 0; y < H; ++y)
+        for (int x = 0; x < W; ++x) {
+            const size_t o = ((size_t)y * W + x) * HD;
+            for (int d = 0; d < HD; ++d) {
+                const real an = A[o + d];
+                real acc = 0;
+                for (int dy = -1; dy <= 1; ++dy)
+                    for (int dx = -1; dx <= 1; ++dx) {
+                        const size_t s = ((size_t)wrap(y + dy, H) * W + wrap(x + dx, W)) * HD + d;
+                        acc += r_exp(an - mx[s]) / den[s] * V[s];
+                    }
+                Vp[o + d] = acc;
+            }
+        }
+}
+
+/* ---- stages 5-6, closed form: E = exp(A), Z = box3(E), R = V/Z, V' = E * box3(R).  Same function as the
+ * literal form (the softmax's max cancels); used by the timed CPU baseline and checked against it. ---- */
+static void redistribute_boxsum(const real* A, const real* V, int H, int W, real* E, real* R, real* Vp) {
+    const size_t n = (size_t)H * W * HD;
+#pragma omp parallel for schedule(static)
+    for (size_t i = 0; i < n; ++i) E[i] = r_exp(A[i]);
+#pragma omp parallel for schedule(static)
+    for (int y = 0; y < H; ++y)
+        for (int x = 0; x < W; ++x) {
+            const size_t o = ((size_t)y * W + x) * HD;
+            real z[HD];
+            for (int d = 0; d < HD; ++d) z[d] = 0;
+            for (int dy = -1; dy <= 1; ++dy)
+                for (int dx = -1; dx <= 1; ++dx) {
+                    const real* e = E + ((size_t)wrap(y + dy, H) * W + wrap(x + dx, W)) * HD;
+                    for (int d = 0; d < HD; ++d) z[d] += e[d];
+                }
+            for (int d = 0; d < HD; ++d) R[o + d] = V[o + d] / z[d];
+        }
+#pragma omp parallel for schedule(static)
+    for (int y = 0; y < H; ++y)
+        for (int x = 0; x < W; ++x) {
+            const size_t o = ((size_t)y * W + x) * HD;
+            real b[HD];
+            for (int d = 0; d < HD; ++d) b[d] = 0;
+            for (int dy = -1; dy <= 1; ++dy)
+                for (int dx = -1; dx <= 1; ++dx) {
+                    const real* r = R + ((size_t)wrap(y + dy, H) * W + wrap(x + dx, W)) * HD;
+                    for (int d = 0; d < HD; ++d) b[d] += r[d];
+                }
+            for (int d = 0; d < HD; ++d) Vp[o + d] = E[o + d] * b[d];
+        }
+}
+
+/* ---- stage 7 for one head: Y += V'_h Wo_h ---- */
+static void output_head(const real* Vp, int cells, const weight_set* w, int h, real* Y) {
+    const float* wo = w->Wo + (size_t)h * HD * NC;
+#pragma omp parallel for schedule(static)
+    for (int s = 0; s < cells; ++s) {
+        real acc[NC];
+        real* y = Y + (size_t)s * NC;
+        for (int c = 0; c < NC; ++c) acc[c] = y[c];
+        const real* v = Vp + (size_t)s * HD;
+        for (int d = 0; d < HD; ++d) {
+            const real vd = v[d];
+            const float* r = wo + d * NC;
+            for (int c = 0; c < NC; ++c) acc[c] += vd * (real)r[c];
+        }
+        for (int c = 0; c < NC; ++c) y[c] = acc[c];
+    }
+}
+
+/* Per-channel sums of one grid, fp64, fixed order (row by row). */
+static void channel_sums(const float* X, int cells, double* out) {
+    for (int c = 0; c < NC; ++c) out[c] = 0;
+    for (int s = 0; s < cells; ++s)
+        for (int c = 0; c < NC; ++c) out[c] += (double)X[(size_t)s * NC + c];
+}
+
+/*
+ * Per-channel masses of every grid: mass[b][c] = sum over cells of X[b,:,:,c]  (fp64).
+ */
+void oracle_channel_mass(const float* X, int B, int H, int W, double* mass) {
+    for (int b = 0; b < B; ++b) channel_sums(X + (size_t)b * H * W * NC, H * W, mass + (size_t)b * NC);
+}
+
+/*
+ * Run n_steps of the contract step on B independent grids, in place.
+ *   X        [B][H][W][64] fp32, in/out
+ *   mass     [B][64] target per-channel masses (M_c); NULL = take them from X at entry
+ *   sets     n_sets weight sets given as seven arrays, each the concatenation over sets
+ *            grid b uses set b / (B / n_sets)
+ *   literal  1 = stages 5-6 as the per-source softmax scatter; 0 = closed box-sum form
+ *   renorm   1 = apply stage 9 after every step
+ *   vp_prev, vp_last  optional [B][H][W][512] fp32: V' (index h*64+d) of steps n_steps-1 and n_steps
+ * Returns 0, or -1 on bad arguments / allocation failure.
+ */
+int oracle_ca_steps(float* X, const double* mass, int B, int H, int W,
+                    const float* Wp, const float* Wi, const float* Wv, const float* Wo,
+                    const float* K, const float* mu, const float* sigma, int n_sets,
+                    int n_steps, float dt, int literal, int renorm,
+                    float* vp_prev, float* vp_last) {
+    if (!X || B <= 0 || H <= 0 || W <= 0 || n_sets <= 0 || B % n_sets != 0 || n_steps < 0) return -1;
+    const int cells = H * W;
+    const size_t n = (size_t)cells * HD;
+    real* P = (real*)malloc(n * sizeof(real));
+    real* I = (real*)malloc(n * sizeof(real));
+    real* V = (real*)malloc(n * sizeof(real));
+    real* A = (real*)malloc(n * sizeof(real));
+    real* T0 = (real*)malloc(n * sizeof(real));
+    real* T1 = (real*)malloc(n * sizeof(real));
+    real* Vp = (real*)malloc(n * sizeof(real));
+    real* Y = (real*)malloc((size_t)cells * NC * sizeof(real));
+    double* M = (double*)malloc((size_t)B * NC * sizeof(double));
+    if (!P || !I || !V || !A || !T0 || !T1 || !Vp || !Y || !M) {
+        free(P); free(I); free(V); free(A); free(T0); free(T1); free(Vp); free(Y); free(M);
+        return -1;
+    }
+    if (mass) memcpy(M, mass, (size_t)B * NC * sizeof(double));
+    else oracle_channel_mass(X, B, H, W, M);
+    const int per_set = B / n_sets;
+
+    for (int b = 0; b < B; ++b) {
+        const int si = b / per_set;
+        weight_set w = { Wp + (size_t)si * NH * NC * HD, Wi + (size_t)si * NH * NC * HD,
+                         Wv + (size_t)si * NH * NC * HD, Wo + (size_t)si * HC * NC,
+                         K + (size_t)si * NH * 9, mu + (size_t)si * NH, sigma + (size_t)si * NH };
+        float* Xb = X + (size_t)b * cells * NC;
+        for (int step = 0; step < n_steps; ++step) {
+            memset(Y, 0, (size_t)cells * NC * sizeof(real));
+            for (int h = 0; h < NH; ++h) {
+                project_head(Xb, cells, &w, h, P, I, V);
+                activation_head(P, I, H, W, &w, h, A);
+                if (literal) redistribute_literal(A, V, H, W, T0, T1, Vp);
+                else redistribute_boxsum(A, V, H, W, T0, T1, Vp);
+                output_head(Vp, cells, &w, h, Y);
+                float* dst = NULL;
+                if (step == n_steps - 1 && vp_last) dst = vp_last;
+                if (step == n_steps - 2 && vp_prev) dst = vp_prev;
+                if (dst) {
+                    dst += (size_t)b * cells * HC;
+                    for (int s = 0; s < cells; ++s)
+                        for (int d = 0; d < HD; ++d) dst[(size_t)s * HC + h * HD + d] = (float)Vp[(size_t)s * HD + d];
+                }
+            }
+            /* stage 8 */
+            for (size_t i = 0; i < (size_t)cells * NC; ++i) Xb[i] = (float)((real)Xb[i] + (real)dt * Y[i]);
+            /* stage 9 */
+            if (renorm) {
+                double s[NC];
+                channel_sums(Xb, cells, s);
+                for (int c = 0; c < NC; ++c) s[c] = M[(size_t)b * NC + c] / s[c];
+                for (int q = 0; q < cells; ++q)
+                    for (int c = 0; c < NC; ++c) Xb[(size_t)q * NC + c] = (float)((double)Xb[(size_t)q * NC + c] * s[c]);
+            }
+        }
+    }
+    free(P); free(I); free(V); free(A); free(T0); free(T1); free(Vp); free(Y); free(M);
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* Fitness                                                                                           */
+/* ------------------------------------------------------------------------------------------------ */
+
+/*
+ * Eigenvalues of a symmetric n x n matrix by cyclic two-sided Jacobi (in place; fp64).
+ * Rotation: tau = (aqq-app)/(2 apq), t = sign(tau)/(|tau|+sqrt(1+tau^2)), c = 1/sqrt(1+t^2), s = t c
+ * (slime/kernels/warp_ca.cu:51-63).  At most 30 sweeps (warp_ca.cu:20), stopping once the
+ * off-diagonal Frobenius norm is <= 1e-6 x the matrix Frobenius norm (tolerance of
+ * failed_attempts/pseudopod.cu:367, made scale-free).  Returns the number of sweeps done.
+ */
+int oracle_jacobi_eigenvalues(double* A, int n, double* eig) {
+    double fro = 0;
+    for (int i = 0; i < n * n; ++i) fro += A[i] * A[i];
+    fro = sqrt(fro);
+    int sweep = 0;
+    for (; sweep < 30; ++sweep) {
+        double off = 0;
+        for (int p = 0; p < n; ++p)
+            for (int q = 0; q < n; ++q)
+                if (p != q) off += A[p * n + q] * A[p * n + q];
+        if (sqrt(off) <= 1e-6 * fro) break;
+        for (int p = 0; p < n - 1; ++p)
+            for (int q = p + 1; q < n; ++q) {
+                const double apq = A[p * n + q];
+                if (apq == 0.0) continue;
+                const double app = A[p * n + p], aqq = A[q * n + q];
+                const double tau = (aqq - app) / (2.0 * apq);
+                const double t = (tau >= 0 ? 1.0 : -1.0) / (fabs(tau) + sqrt(1.0 + tau * tau));
+                const double c = 1.0 / sqrt(1.0 + t * t), s = t * c;
+                for (int k = 0; k < n; ++k) { /* columns p,q */
+                    const double akp = A[k * n + p], akq = A[k * n + q];
+                    A[k * n + p] = c * akp - s * akq;
+                    A[k * n + q] = s * akp + c * akq;
+                }
+                for (int k = 0; k < n; ++k) { /* rows p,q */
+                    const double apk = A[p * n + k], aqk = A[q * n + k];
+                    A[p * n + k] = c * apk - s * aqk;
+                    A[q * n + k] = s * apk + c * aqk;
+                }
+            }
+    }
+    for (int i = 0; i < n; ++i) eig[i] = A[i * n + i];
+    return sweep;
+}
+
+/*
+ * exp-entropy rank of a spectrum: clamp to >= 0, p = l/(sum l + 1e-7), rank = exp(-sum p ln(p + 1e-7))
+ * (slime/kernels/warp_ca.cu:107-144, epsilon :21).
+ */
+double oracle_entropy_rank(const double* eig, int n) {
+    double sum = 0;
+    for (int i = 0; i < n; ++i) sum += eig[i] > 0 ? eig[i] : 0;
+    double ent = 0;
+    for (int i = 0; i < n; ++i) {
+        const double p = (eig[i] > 0 ? eig[i] : 0) / (sum + 1e-7);
+        ent -= p * log(p + 1e-7);
+    }
+    return exp(ent);
+}
+
+/* Gram matrices of one grid's V' : gram[h][i][j] = sum_cells F[s][h*64+i] F[s][h*64+j]  (fp64). */
+void oracle_gram(const float* vp, int cells, double* gram) {
+#pragma omp parallel for schedule(static)
+    for (int h = 0; h < NH; ++h) {
+        double* g = gram + (size_t)h * HD * HD;
+        for (int i = 0; i < HD * HD; ++i) g[i] = 0;
+        for (int s = 0; s < cells; ++s) {
+            const float* f = vp + (size_t)s * HC + h * HD;
+            for (int i = 0; i < HD; ++i) {
+                const double fi = f[i];
+                for (int j = 0; j < HD; ++j) g[i * HD + j] += fi * (double)f[j];
+            }
+        }
+    }
+}
+
+/*
+ * Fitness of B grids from V' at the last two steps ([B][cells][512] fp32 each).
+ * out_rank[b]  = mean over heads of the exp-entropy rank of that head's Gram spectrum
+ * out_coh[b]   = Pearson r between all cells x 512 elements of vp_prev and vp_last (BLUEPRINT.md:362,428)
+ * out_fit[b]   = rank x coherence (slime/kernels/warp_ca.cu:219); out_hunger[b] = 1 - coherence (:238)
+ * out_head_rank optional [B][8].
+ */
+int oracle_fitness(const float* vp_prev, const float* vp_last, int B, int cells,
+                   float* out_rank, float* out_coh, float* out_fit, float* out_hunger, float* out_head_rank) {
+    if (!vp_prev || !vp_last || B <= 0 || cells <= 0) return -1;
+    double* gram = (double*)malloc((size_t)NH * HD * HD * sizeof(double));
+    if (!gram) return -1;
+    for (int b = 0; b < B; ++b) {
+        const float* a = vp_prev + (size_t)b * cells * HC;
+        const float* c = vp_last + (size_t)b * cells * HC;
+        oracle_gram(c, cells, gram);
+        double rk = 0;
+        for (int h = 0; h < NH; ++h) {
+            double eig[HD];
+            oracle_jacobi_eigenvalues(gram + (size_t)h * HD * HD, HD, eig);
+            const double r = oracle_entropy_rank(eig, HD);
+            if (out_head_rank) out_head_rank[(size_t)b * NH + h] = (float)r;
+            rk += r;
+        }
+        rk /= NH;
+        const size_t n = (size_t)cells * HC;
+        double sa = 0, sb = 0;
+        for (size_t i = 0; i < n; ++i) { sa += a[i]; sb += c[i]; }
+        const double ma = sa / (double)n, mb = sb / (double)n;
+        double saa = 0, sbb = 0, sab = 0;
+        for (size_t i = 0; i < n; ++i) {
+            const double da = a[i] - ma, db = c[i] - mb;
+            saa += da * da; sbb += db * db; sab += da * db;
+        }
+        const double coh = sab / sqrt(saa * sbb);
+        if (out_rank) out_rank[b] = (float)rk;
+        if (out_coh) out_coh[b] = (float)coh;
+        if (out_fit) out_fit[b] = (float)(rk * coh);
+        if (out_hunger) out_hunger[b] = (float)(1.0 - coh);
+    }
+    free(gram);
+    return 0;
+}
+
+/* ------------------------------------------------------------------------------------------------ */
+/* Field <-> CA coupling (the step's two neighbours in the reference driver)                         */
+/* ------------------------------------------------------------------------------------------------ */
+
+/*
+ * Lift a one-channel field into the 64-channel CA state: X[b,y,x,c] = img[b,y,x] * L[c], after zero-padding
+ * the image by `pad` pixels on every side.  Mirrors slime/core/organism.cu:691-720, which lifts the chemical
+ * field with a fixed per-channel factor.
+ */
+void oracle_lift(const float* img, int B, int h, int w, int pad, const float* L, float* X) {
+    const int H = h + 2 * pad, W = w + 2 * pad;
+    memset(X, 0, (size_t)B * H * W * NC * sizeof(float));
+    for (int b = 0; b < B; ++b)
+        for (int y = 0; y < h; ++y)
+            for (int x = 0; x < w; ++x) {
+                const float v = img[((size_t)b * h + y) * w + x];
+                float* o = X + (((size_t)b * H + y + pad) * W + x + pad) * NC;
+                for (int c = 0; c < NC; ++c) o[c] = v * L[c];
+            }
+}
+
+/*
+ * Mean-pool the state over space and apply a 64 -> n_out linear readout:
+ * logits[b][o] = sum_c mean_cells(X[b,:,:,c]) Wr[c][o] + br[o].  The pooling mirrors
+ * slime/core/organism.cu:723-743 (mean write-back of the CA into the field).
+ */
+void oracle_pool_readout(const float* X, int B, int cells, const float* Wr, const float* br, int n_out, float* logits) {
+    for (int b = 0; b < B; ++b) {
+        double m[NC];
+        channel_sums(X + (size_t)b * cells * NC, cells, m);
+        for (int o = 0; o < n_out; ++o) {
+            double acc = br ? br[o] : 0.0;
+            for (int c = 0; c < NC; ++c) acc += m[c] / cells * (double)Wr[c * n_out + o];
+            logits[(size_t)b * n_out + o] = (float)acc;
+        }
+    }
+}
