@@ -1,0 +1,236 @@
+#!/usr/bin/env python
+"""Throughput of the Flow-Lenia CA step in cell-updates/s.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--dtype bf16|f32] [--impl ours|reference]
+
+Workload (N=1 and every N, weak scaling: each rank steps its own batch, no data-path collective): the batched
+training-shape forward X[64,128,128,64], bf16 storage / fp32 accumulate, 8 heads x 64, 64 CA steps per bench
+step, seeded synthetic state (uniform, unit mass per channel) and one seeded weight set.  One bench "step" is
+one such 64-step forward.  `value` is timed with the state resident in HBM; `e2e` copies the state in from
+pinned host memory and back out through the C ABI inside the timed region.
+
+`--impl reference` times the CPU transcription of the same step (the reference has no CPU path and no runnable
+GPU step; the transcription is the oracle's fp32 build, all host threads) on a bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "CA cell-updates/sec"
+UNIT = "cell-updates/s"
+GRID, BATCH, CA_STEPS = 128, 64, 64
+# algorithmic HBM bytes per cell-update of each kernel (bf16 / f32 storage): k1 reads the state (64 values) and
+# writes E and V (2 x 512 values); k2 reads E and V and reads + writes the state.
+ALG_BYTES = {"k1": {"bf16": 128 + 2048, "f32": 256 + 4096}, "k2": {"bf16": 2048 + 256, "f32": 4096 + 512}}
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.rows, self._stop = index, [], threading.Event()
+
+    def run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                f = [x.strip() for x in out.strip().split(",")]
+                if len(f) == 6:
+                    self.rows.append(f)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def stop(self):
+        self._stop.set()
+        self.join(timeout=6)
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(r[0]) for r in self.rows)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def cpu_baseline(ca_steps_sample=2, grids=1):
+    """The oracle's fp32 multithreaded transcription on a bounded sample: `grids` grids x `ca_steps_sample` steps."""
+    from oracle import ca_oracle
+    from slime_b200 import inputs
+    X = inputs.make_state(grids, GRID, GRID, seed=42)
+    w = inputs.make_weight_sets(1, seed=42)
+    ca_oracle.ca_steps(X[:1, :16, :16].copy(), w, 1, literal=False, real="f32")       # load + warm the library
+    t0 = time.perf_counter()
+    ca_oracle.ca_steps(X, w, ca_steps_sample, literal=False, real="f32")
+    dt = time.perf_counter() - t0
+    cores = len(os.sched_getaffinity(0))
+    return {"value": grids * GRID * GRID * ca_steps_sample / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{grids} grid(s) of {GRID}x{GRID}x64, {ca_steps_sample} CA steps, fp32, OpenMP on {cores} threads "
+                      f"({dt:.1f} s)"}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    per_step = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_baseline(ca_steps_sample=2, grids=1)
+        if i >= args.warmup:
+            per_step.append(base["value"])
+    v = float(np.mean(per_step))
+    base["value"] = v
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": BATCH * GRID * GRID * CA_STEPS / v * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"X[{BATCH},{GRID},{GRID},64] x {CA_STEPS} CA steps (bounded sample per step, rate extrapolated)",
+                       "inputs": "seeded synthetic"},
+            "cpu_baseline": base,
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--dtype", choices=["bf16", "f32"], default="bf16")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=BATCH)
+    ap.add_argument("--ca-steps", type=int, default=CA_STEPS)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    from slime_b200 import capi, inputs
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.warmup < 3:
+        args.warmup = 3
+
+    B, S = args.batch, args.ca_steps
+    dt_code = capi.BF16 if args.dtype == "bf16" else capi.F32
+    tdt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    h = capi.Handle(B, GRID, GRID, n_weight_sets=1, dtype=dt_code, device=local)
+    h.set_weights(inputs.make_weight_sets(1, seed=42))
+    X0 = inputs.make_state(B, GRID, GRID, seed=42, first_grid=rank * B)
+    host = torch.from_numpy(X0).to(tdt).pin_memory()
+    host_out = torch.empty_like(host).pin_memory()
+    state_bytes = host.numel() * host.element_size()
+    stream = torch.cuda.current_stream().cuda_stream
+    cells = B * GRID * GRID
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # ---- device-resident throughput -------------------------------------------------------------
+    h.set_state_ptr(host.data_ptr(), dt_code, stream)
+    for _ in range(args.warmup):
+        h.step(S, stream)
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    l0 = h.launch_count
+    ms = timed(lambda: h.step(S, stream), args.steps)
+    launches = h.launch_count - l0
+    clocks = sampler.stop() if sampler else None
+    value = world * cells * S * args.steps / (ms * 1e-3)
+
+    # ---- per-kernel time of the same step loop (CUDA events between the kernels, on the launch stream) ----
+    kt = h.step_timed(S, stream)          # ms summed over the S steps: k1, k2, reductions
+    dom = "k1" if kt[0] >= kt[1] else "k2"
+    dom_ms = max(kt[0], kt[1]) / S
+    peak, peak_kind = measured_peaks()
+    achieved = cells * ALG_BYTES[dom][args.dtype] / (dom_ms * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                "ms_per_launch": dom_ms, "k1_ms": kt[0] / S, "k2_ms": kt[1] / S, "other_ms": kt[2] / S}
+
+    # ---- end to end through the C ABI: host state in, 64 steps, host state out -------------------
+    def e2e_step():
+        h.set_state_ptr(host.data_ptr(), dt_code, stream)
+        h.step(S, stream)
+        h.get_state_ptr(host_out.data_ptr(), dt_code, stream)
+
+    for _ in range(2):
+        e2e_step()
+    ms_e2e = timed(e2e_step, args.steps)
+    e2e = {"value": world * cells * S * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
+           "h2d_bytes_per_step": state_bytes, "d2h_bytes_per_step": state_bytes}
+    finite = bool(torch.isfinite(host_out.float()).all())
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
+                "config": {"workload": f"batched training-shape forward X[{B},{GRID},{GRID},64] per GPU, 8 heads x 64, "
+                                       f"{S} CA steps per bench step, renorm every step",
+                           "l2": "working set per step (E,V intermediates %.1f GB) exceeds the 126 MB L2" %
+                                 (2 * cells * 512 * (2 if args.dtype == "bf16" else 4) / 1e9),
+                           "parallelism": f"batch-sharded x{world}, no data-path collective"},
+                "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
+                "outputs_finite": finite}
+        if not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(ca_steps_sample=4, grids=2)
+        print(json.dumps(line), flush=True)
+    h.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

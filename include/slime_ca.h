@@ -1,0 +1,173 @@
+/*
+ * slime_ca.h - C ABI of the B200 (sm_100a) multi-head Flow-Lenia neural-CA step.
+ *
+ * This is the boundary a J0pari/Slime maintainer binds instead of the CA kernels of
+ * slime/core/pseudopod.cu and their device-side driver in slime/core/organism.cu.  Plain pointers and sizes
+ * only; every call returns an int status (0 = ok) and never exits the process (the reference's CUDA_CHECK,
+ * slime/runtime.cu:11-20, prints and calls exit(1)).
+ *
+ * One handle drives one GPU.  A handle owns its state, intermediates and workspace; the caller owns every
+ * pointer it passes in.  slime_ca_step() allocates nothing.  Calls on one handle must not overlap; different
+ * handles are independent.  `stream` arguments are a cudaStream_t passed as void* (NULL = default stream).
+ */
+#ifndef SLIME_CA_H
+#define SLIME_CA_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SLIME_CA_NUM_HEADS 8   /* slime/core/pseudopod.cu:15 NUM_HEADS */
+#define SLIME_CA_HEAD_DIM 64   /* slime/core/pseudopod.cu:16 HEAD_DIM  */
+#define SLIME_CA_CHANNELS 64   /* channels of the state the step reads and writes */
+
+enum slime_ca_status {
+    SLIME_CA_OK = 0,
+    SLIME_CA_EINVAL = 1,  /* bad argument (null pointer, bad shape, index out of range)          */
+    SLIME_CA_ECUDA = 2,   /* a CUDA runtime call failed; slime_ca_last_error() has the text       */
+    SLIME_CA_ENOMEM = 3,  /* host or device allocation failed                                     */
+    SLIME_CA_ESTATE = 4,  /* call order: weights or state not set, fitness before two steps, ...  */
+    SLIME_CA_EDEVICE = 5  /* a kernel reported an error through its status word (bounded wait ran out) */
+};
+
+enum slime_ca_dtype {
+    SLIME_CA_F32 = 0,  /* fp32 storage and arithmetic (SIMT)                                             */
+    SLIME_CA_BF16 = 1  /* bf16 storage of state/weights/intermediates, fp32 accumulate, tcgen05 projections */
+};
+
+enum slime_ca_buffer {
+    SLIME_CA_BUF_STATE = 0,       /* [batch][height + 2*halo][width][64], dtype of the handle, un-normalised */
+    SLIME_CA_BUF_SCALE = 1,       /* [batch][64] fp32: true state = stored state * scale                     */
+    SLIME_CA_BUF_MASS = 2,        /* [batch][64] fp64: target per-channel masses                             */
+    SLIME_CA_BUF_SUMS = 3,        /* [batch][64] fp64: per-channel sums of the stored state's own rows       */
+    SLIME_CA_BUF_VPRIME_PREV = 4, /* [batch][8][height][width][64]: redistributed value of step n-1         */
+    SLIME_CA_BUF_VPRIME_LAST = 5  /* same, step n                                                            */
+};
+
+/*
+ * Replaces the fixed constexpr configuration of slime/core/pseudopod.cu:15-21 (GRID_SIZE = 128, batch 1).
+ */
+typedef struct slime_ca_config {
+    int batch;          /* independent grids held by this handle                                          */
+    int height;         /* rows per grid owned by this handle                                             */
+    int width;          /* columns per grid                                                               */
+    int n_weight_sets;  /* grid b uses weight set b / (batch / n_weight_sets); must divide batch           */
+    int dtype;          /* enum slime_ca_dtype                                                            */
+    float dt;           /* residual step size; the reference uses 0.1 (slime/core/organism.cu:659)        */
+    int device;         /* CUDA device ordinal                                                            */
+    int stripe;         /* 0: every grid is a full torus.  1: the grid is a row stripe of a taller torus:  */
+                        /*    the state buffer carries 3 halo rows above and below the `height` own rows,  */
+                        /*    which the caller refreshes before every step (x still wraps)                 */
+    int keep_vprime;    /* 1: keep the redistributed value V' of the last two steps (needed by fitness)    */
+} slime_ca_config;
+
+typedef struct slime_ca slime_ca;
+
+/* Handle lifetime.  Replaces the CA part of create_organism()/destroy_organism() (slime/runtime.cu:26,417:
+ * cudaMalloc of weights, ca_input, ca_output, mass_buffer at slime/runtime.cu:66-94). */
+int slime_ca_create(const slime_ca_config* cfg, slime_ca** out);
+int slime_ca_destroy(slime_ca* h);
+
+/* Text of the last failure on this handle (never NULL).  The reference has no status channel. */
+const char* slime_ca_last_error(const slime_ca* h);
+
+/* Device bytes the handle holds (state + intermediates + workspace).  Backs KernelProtocol::memory_required()
+ * (slime/proto/kernel.cu:13). */
+size_t slime_ca_workspace_bytes(const slime_ca* h);
+
+/*
+ * Upload one weight set from HOST fp32 arrays in the reference's index order (slime/core/pseudopod.cu:86-87):
+ *   Wp, Wi, Wv [8][64][64] = [head][c_in][d_out];  Wo [512][64] = [head*64+d][c_out];
+ *   K [8][9] taps t=(dy+1)*3+(dx+1) (slime/core/pseudopod.cu:153);  mu, sigma [8] growth centre and width.
+ * Replaces init_multihead_ca_kernel (slime/core/pseudopod.cu:386-444) as the way weights reach the device.
+ */
+int slime_ca_set_weights(slime_ca* h, int set_index, const float* Wp, const float* Wi, const float* Wv,
+                         const float* Wo, const float* K, const float* mu, const float* sigma);
+
+/*
+ * Load / read the state from HOST memory, [batch][height][width][64] in `host_dtype` (fp32 or bf16).
+ * set_state also records each (grid, channel) sum as its target mass.  get_state returns the normalised
+ * state (stored state * scale).  Replaces initialize_ca_from_field / get_ca_state as the way state enters
+ * and leaves (slime/core/organism.cu:691-720, slime/runtime.cu:479-504).  Both synchronise `stream`.
+ */
+int slime_ca_set_state(slime_ca* h, const void* host_state, int host_dtype, void* stream);
+int slime_ca_get_state(slime_ca* h, void* host_state, int host_dtype, void* stream);
+
+/* Same with DEVICE pointers (no synchronisation). */
+int slime_ca_set_state_device(slime_ca* h, const void* dev_state, int dtype, void* stream);
+int slime_ca_get_state_device(slime_ca* h, void* dev_state, int dtype, void* stream);
+
+/* Override / read the target masses, HOST fp64 [batch][64] (stripe mode: the caller supplies global sums). */
+int slime_ca_set_mass(slime_ca* h, const double* mass);
+int slime_ca_get_mass(slime_ca* h, double* mass);
+
+/*
+ * n_steps of the CA step on every grid of the handle, enqueued on `stream`; returns without synchronising.
+ * Replaces neural_ca_update_kernel and the three kernels it launches (slime/core/organism.cu:617-688;
+ * slime/core/pseudopod.cu:41-131, 134-214, 217-253).
+ */
+int slime_ca_step(slime_ca* h, int n_steps, void* stream);
+
+/*
+ * Stripe mode, several ranks: one step split around the caller's all-reduce.
+ *   slime_ca_step_partial  runs the step's kernels and leaves this rank's per-channel sums in BUF_SUMS;
+ *   (caller sums BUF_SUMS over ranks, e.g. ncclAllReduce, and refreshes the halo rows of BUF_STATE)
+ *   slime_ca_step_finish   turns BUF_SUMS and BUF_MASS into the new BUF_SCALE.
+ * slime_ca_step(h, 1, s) equals partial followed by finish.
+ */
+int slime_ca_step_partial(slime_ca* h, void* stream);
+int slime_ca_step_finish(slime_ca* h, void* stream);
+
+/*
+ * Profiling aid with no counterpart in the reference: n_steps steps with CUDA events recorded on `stream`
+ * around each kernel; ms[0..2] receive the summed device time of the projection/growth kernel, of the
+ * redistribution/output kernel and of the reduction + scale kernels.  Synchronises `stream`.
+ */
+int slime_ca_step_timed(slime_ca* h, int n_steps, void* stream, float* ms);
+
+/* Device address and size of one of the handle's buffers (enum slime_ca_buffer), for halo exchange,
+ * all-reduce and zero-copy views.  The reference exposes raw device pointers in MultiHeadCAState
+ * (slime/core/pseudopod.cu:29-38). */
+int slime_ca_buffer(slime_ca* h, int which, void** dev_ptr, size_t* bytes);
+
+/*
+ * Fitness of every grid from V' of the last two steps (needs keep_vprime and at least two steps):
+ * HOST fp32 arrays of `batch` elements, any of which may be NULL.  rank = mean over heads of the
+ * exp-entropy rank of that head's 64x64 Gram spectrum (Jacobi), coherence = Pearson r between the two
+ * steps, fitness = rank * coherence, hunger = 1 - coherence.  Replaces fitness_fused_kernel and its
+ * children (slime/kernels/warp_ca.cu:66-226) and the hunger kernel (:229-240).  Synchronises `stream`.
+ */
+int slime_ca_fitness(slime_ca* h, float* rank, float* coherence, float* fitness, float* hunger, void* stream);
+
+/* Lift a one-channel HOST image batch [batch][img_h][img_w] (fp32) into the state: zero-pad to
+ * height x width (centred), X = pixel * L[c].  Mirrors initialize_ca_from_field_kernel
+ * (slime/core/organism.cu:691-720). */
+int slime_ca_lift_images(slime_ca* h, const float* host_img, int img_h, int img_w, const float* host_L,
+                         void* stream);
+
+/* Mean-pool the normalised state over space and apply a 64 -> n_out linear readout (HOST fp32 Wr[64][n_out],
+ * br[n_out] or NULL) into HOST logits[batch][n_out].  The pooling mirrors update_field_from_ca_kernel
+ * (slime/core/organism.cu:723-743). */
+int slime_ca_pool_readout(slime_ca* h, const float* host_Wr, const float* host_br, int n_out,
+                          float* host_logits, void* stream);
+
+/* Number of kernels the library has launched on this handle since creation (for launch accounting). */
+long long slime_ca_launch_count(const slime_ca* h);
+
+/*
+ * The host launcher the reference planned but never wrote (buildplan.md:635-655):
+ *   ca_state  device fp32 [batch][grid][grid][64]
+ *   weights   device fp32 [P | I | V], each [8][64][64]
+ *   ca_output device fp32 [batch][8][grid][grid][64]: each head's redistributed value V'
+ * Flow kernels are uniform (1/9 per tap) and the growth uses mu = 0.2, sigma = 0.03, the midpoints of the
+ * ranges the weights are drawn from, because the planned signature carries neither.  Runs on the default
+ * stream and synchronises.  Returns nothing, as planned; errors are printed to stderr.
+ */
+void launch_multi_head_ca(float* ca_state, float* weights, float* ca_output, int batch_size, int grid_size);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SLIME_CA_H */

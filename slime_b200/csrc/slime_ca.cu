@@ -1,0 +1,617 @@
+// C ABI of the B200 Flow-Lenia CA step (see include/slime_ca.h): handle, buffers, launch sequencing.
+// Host-side step driver: what neural_ca_update_kernel (slime/core/organism.cu:617-688) does from a device
+// thread with dynamic parallelism is sequenced here from the host on one stream.
+#include "../../include/slime_ca.h"
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "ca_aux.cuh"
+#include "ca_bf16.cuh"
+#include "ca_f32.cuh"
+#include "common.cuh"
+#include "fitness.cuh"
+
+using namespace slime;
+
+struct slime_ca {
+    slime_ca_config cfg{};
+    Geom g{};
+    size_t esz = 4;                 // bytes per stored element
+    void* X = nullptr;              // [B][H+2hx][W][64]
+    void* E = nullptr;              // [B][8][H+2he][W][64]
+    void* V = nullptr;
+    void* vprime[2] = {nullptr, nullptr};
+    int vp_last = 0;                // index of the buffer holding the most recent V'
+    long long steps_done = 0, vp_steps = 0;
+    float* scale = nullptr;
+    double* mass = nullptr;
+    double* sums = nullptr;
+    float* partial = nullptr;
+    int partial_cap = 0;
+    double* seg_sums = nullptr;
+    int k1_tiles = 0, k2_tiles = 0, tiles_x = 0;
+    // weights
+    float* wpiv_f32 = nullptr;      // [sets][8][64][192]  rows c_in, columns Wp | Wi | Wv
+    float* wo_f32 = nullptr;        // [sets][8][64][64]   rows d, columns c_out
+    float* prm = nullptr;           // [sets][8][PRM]
+    __nv_bfloat16* w1_bf16 = nullptr;  // [sets][8][192][64]  rows = output column (Wp|Wi|Wv), K = c_in contiguous
+    __nv_bfloat16* wo_bf16 = nullptr;  // [sets][8][64][64]   rows = c_out, K = d contiguous
+    std::vector<char> weights_set;
+    bool state_set = false;
+    // fitness scratch
+    double* gram_part = nullptr;
+    int gram_splits = 0;
+    float* head_rank = nullptr;
+    double* pearson_part = nullptr;
+    int pearson_splits = 0;
+    float* fit_dev = nullptr;
+    int* dev_status = nullptr;      // status word kernels with bounded waits report into
+    size_t bytes = 0;
+    long long launches = 0;
+    std::string err = "";
+    Bf16Plan bf{};
+};
+
+namespace {
+
+int fail(slime_ca* h, int code, const std::string& msg) {
+    if (h) h->err = msg;
+    return code;
+}
+
+#define CK(h, call)                                                                                   \
+    do {                                                                                              \
+        cudaError_t e_ = (call);                                                                      \
+        if (e_ != cudaSuccess)                                                                        \
+            return fail(h, SLIME_CA_ECUDA, std::string(#call) + ": " + cudaGetErrorString(e_));       \
+    } while (0)
+
+#define LAUNCHED(h)                                                                                   \
+    do {                                                                                              \
+        ++(h)->launches;                                                                              \
+        cudaError_t e_ = cudaGetLastError();                                                          \
+        if (e_ != cudaSuccess)                                                                        \
+            return fail(h, SLIME_CA_ECUDA, std::string("kernel launch: ") + cudaGetErrorString(e_));  \
+    } while (0)
+
+template <typename T>
+int dev_alloc(slime_ca* h, T** p, size_t n) {
+    void* q = nullptr;
+    cudaError_t e = cudaMalloc(&q, n * sizeof(T));
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(h, SLIME_CA_ENOMEM, "cudaMalloc of " + std::to_string(n * sizeof(T)) + " bytes: " + cudaGetErrorString(e));
+    }
+    h->bytes += n * sizeof(T);
+    *p = static_cast<T*>(q);
+    return SLIME_CA_OK;
+}
+
+int grid_for(size_t n) {
+    size_t b = (n + 255) / 256;
+    return (int)(b > 148 * 16 ? 148 * 16 : (b ? b : 1));
+}
+
+bool is_bf16(const slime_ca* h) { return h->cfg.dtype == SLIME_CA_BF16; }
+
+// sums <- per-channel sums of the stored state's own rows; mode as in k_finish_sums
+int channel_sums(slime_ca* h, int mode, cudaStream_t st) {
+    const size_t cells = (size_t)h->g.H * h->g.W;
+    const int chunks = (int)((cells + 255) / 256);
+    dim3 grid(chunks, h->g.B);
+    if (is_bf16(h)) k_channel_partials<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)h->X, h->partial, h->g);
+    else k_channel_partials<float><<<grid, 256, 0, st>>>((const float*)h->X, h->partial, h->g);
+    LAUNCHED(h);
+    const int nseg = chunks < 64 ? chunks : 64;
+    k_reduce_partials<<<dim3(nseg, h->g.B), 256, 0, st>>>(h->partial, chunks, h->seg_sums);
+    LAUNCHED(h);
+    k_finish_sums<<<h->g.B, 64, 0, st>>>(h->seg_sums, nseg, h->sums, h->mass, h->scale, mode);
+    LAUNCHED(h);
+    return SLIME_CA_OK;
+}
+
+// the kernels of one step up to and including BUF_SUMS; `emit` = V' destination or null
+// `ev`, when given, receives three records: before k1, between k1 and k2, after k2
+int step_kernels(slime_ca* h, void* emit, cudaStream_t st, cudaEvent_t* ev = nullptr) {
+    const Geom& g = h->g;
+    if (ev) CK(h, cudaEventRecord(ev[0], st));
+    if (is_bf16(h)) {
+        if (bf16_k1(h->bf, (const __nv_bfloat16*)h->X, h->scale, h->prm, (__nv_bfloat16*)h->E, (__nv_bfloat16*)h->V,
+                    h->dev_status, g, st) != 0)
+            return fail(h, SLIME_CA_ECUDA, std::string("bf16 k1 launch: ") + cudaGetErrorString(cudaGetLastError()));
+        ++h->launches;
+        if (ev) CK(h, cudaEventRecord(ev[1], st));
+        if (bf16_k2(h->bf, (__nv_bfloat16*)h->X, h->scale, (const __nv_bfloat16*)h->E, (const __nv_bfloat16*)h->V,
+                    h->partial, (__nv_bfloat16*)emit, h->dev_status, g, st) != 0)
+            return fail(h, SLIME_CA_ECUDA, std::string("bf16 k2 launch: ") + cudaGetErrorString(cudaGetLastError()));
+        ++h->launches;
+    } else {
+        k1_f32<<<dim3(h->k1_tiles, g.B), 256, K1F32_SMEM, st>>>((const float*)h->X, h->scale, h->wpiv_f32, h->prm,
+                                                                 (float*)h->E, (float*)h->V, g);
+        LAUNCHED(h);
+        if (ev) CK(h, cudaEventRecord(ev[1], st));
+        k2_f32<<<dim3(h->k2_tiles, g.B), 256, K2F32_SMEM, st>>>((float*)h->X, h->scale, h->wo_f32, (const float*)h->E,
+                                                                 (const float*)h->V, h->partial, (float*)emit, g);
+        LAUNCHED(h);
+    }
+    if (ev) CK(h, cudaEventRecord(ev[2], st));
+    const int nseg = h->k2_tiles < 64 ? h->k2_tiles : 64;
+    k_reduce_partials<<<dim3(nseg, g.B), 256, 0, st>>>(h->partial, h->k2_tiles, h->seg_sums);
+    LAUNCHED(h);
+    k_finish_sums<<<g.B, 64, 0, st>>>(h->seg_sums, nseg, h->sums, h->mass, h->scale, 0);
+    LAUNCHED(h);
+    return SLIME_CA_OK;
+}
+
+int ready(slime_ca* h) {
+    if (!h) return SLIME_CA_EINVAL;
+    for (char c : h->weights_set)
+        if (!c) return fail(h, SLIME_CA_ESTATE, "not every weight set has been uploaded");
+    if (!h->state_set) return fail(h, SLIME_CA_ESTATE, "no state has been loaded");
+    return SLIME_CA_OK;
+}
+
+int check_status_word(slime_ca* h) {
+    int s = 0;
+    CK(h, cudaMemcpy(&s, h->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
+    if (s != 0) {
+        cudaMemset(h->dev_status, 0, sizeof(int));
+        return fail(h, SLIME_CA_EDEVICE, "a kernel gave up on a bounded wait (status word " + std::to_string(s) + ")");
+    }
+    return SLIME_CA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
+    if (!cfg || !out) return SLIME_CA_EINVAL;
+    *out = nullptr;
+    if (cfg->batch <= 0 || cfg->height <= 0 || cfg->width <= 0 || cfg->n_weight_sets <= 0 ||
+        cfg->batch % cfg->n_weight_sets != 0 || (cfg->dtype != SLIME_CA_F32 && cfg->dtype != SLIME_CA_BF16) ||
+        (cfg->stripe != 0 && cfg->stripe != 1))
+        return SLIME_CA_EINVAL;
+    int ndev = 0;
+    if (cudaGetDeviceCount(&ndev) != cudaSuccess || cfg->device < 0 || cfg->device >= ndev) {
+        cudaGetLastError();
+        return SLIME_CA_ECUDA;
+    }
+    slime_ca* h = new (std::nothrow) slime_ca();
+    if (!h) return SLIME_CA_ENOMEM;
+    *out = h;  // returned even on failure so that slime_ca_last_error() can be read; destroy it either way
+    h->cfg = *cfg;
+    CK(h, cudaSetDevice(cfg->device));
+    cudaDeviceProp prop{};
+    CK(h, cudaGetDeviceProperties(&prop, cfg->device));
+    if (prop.major != 10) return fail(h, SLIME_CA_ECUDA, "this library is built for sm_100a only; device is sm_" +
+                                                              std::to_string(prop.major) + std::to_string(prop.minor));
+    Geom& g = h->g;
+    g.B = cfg->batch; g.H = cfg->height; g.W = cfg->width;
+    g.hx = cfg->stripe ? 3 : 0; g.he = cfg->stripe ? 2 : 0;
+    g.wrap_y = cfg->stripe ? 0 : 1;
+    g.per_set = cfg->batch / cfg->n_weight_sets;
+    g.dt = cfg->dt;
+    h->esz = cfg->dtype == SLIME_CA_BF16 ? 2 : 4;
+    h->weights_set.assign(cfg->n_weight_sets, 0);
+
+    const size_t xn = (size_t)g.B * g.state_rows() * g.W * NC;
+    const size_t en = (size_t)g.B * NH * g.ev_rows() * g.W * HD;
+    int rc;
+    if (is_bf16(h)) {
+        bf16_plan(h->bf, g);
+        g.tiles_x = h->bf.tiles_x;
+        h->k1_tiles = h->bf.k1_tiles; h->k2_tiles = h->bf.k2_tiles;
+    } else {
+        g.tiles_x = (g.W + T32 - 1) / T32;
+        h->k1_tiles = g.tiles_x * ((g.ev_rows() + T32 - 1) / T32);
+        h->k2_tiles = g.tiles_x * ((g.H + T32 - 1) / T32);
+        CK(h, cudaFuncSetAttribute(k1_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, K1F32_SMEM));
+        CK(h, cudaFuncSetAttribute(k2_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, K2F32_SMEM));
+    }
+    h->tiles_x = g.tiles_x;
+    const int chunks = (int)(((size_t)g.H * g.W + 255) / 256);
+    h->partial_cap = h->k2_tiles > chunks ? h->k2_tiles : chunks;
+
+    char* p = nullptr;
+    if ((rc = dev_alloc(h, &p, xn * h->esz))) return rc; h->X = p;
+    if ((rc = dev_alloc(h, &p, en * h->esz))) return rc; h->E = p;
+    if ((rc = dev_alloc(h, &p, en * h->esz))) return rc; h->V = p;
+    CK(h, cudaMemset(h->X, 0, xn * h->esz));
+    if (cfg->keep_vprime) {
+        const size_t vn = (size_t)g.B * NH * g.H * g.W * HD;
+        for (int i = 0; i < 2; ++i) { if ((rc = dev_alloc(h, &p, vn * h->esz))) return rc; h->vprime[i] = p; }
+        const size_t cells = (size_t)g.H * g.W;
+        h->gram_splits = (int)((cells + GRAM_CHUNK - 1) / GRAM_CHUNK);
+        if (h->gram_splits > 64) h->gram_splits = 64;   // k_gram then covers GRAM_CHUNK * 64 cells at most
+        if ((size_t)h->gram_splits * GRAM_CHUNK < cells)
+            return fail(h, SLIME_CA_EINVAL, "keep_vprime supports grids of at most 131072 cells");
+        if ((rc = dev_alloc(h, &h->gram_part, (size_t)g.B * NH * h->gram_splits * HD * HD))) return rc;
+        if ((rc = dev_alloc(h, &h->head_rank, (size_t)g.B * NH))) return rc;
+        h->pearson_splits = (int)((cells * HC + 262143) / 262144);
+        if (h->pearson_splits > 64) h->pearson_splits = 64;
+        if ((rc = dev_alloc(h, &h->pearson_part, (size_t)g.B * h->pearson_splits * 5))) return rc;
+        if ((rc = dev_alloc(h, &h->fit_dev, (size_t)g.B * 4))) return rc;
+    }
+    if ((rc = dev_alloc(h, &h->scale, (size_t)g.B * NC))) return rc;
+    if ((rc = dev_alloc(h, &h->mass, (size_t)g.B * NC))) return rc;
+    if ((rc = dev_alloc(h, &h->sums, (size_t)g.B * NC))) return rc;
+    if ((rc = dev_alloc(h, &h->partial, (size_t)g.B * h->partial_cap * NC))) return rc;
+    if ((rc = dev_alloc(h, &h->seg_sums, (size_t)g.B * 64 * NC))) return rc;
+    if ((rc = dev_alloc(h, &h->dev_status, 1))) return rc;
+    CK(h, cudaMemset(h->dev_status, 0, sizeof(int)));
+    const size_t sets = cfg->n_weight_sets;
+    if ((rc = dev_alloc(h, &h->prm, sets * NH * PRM))) return rc;
+    if (is_bf16(h)) {
+        if ((rc = dev_alloc(h, &h->w1_bf16, sets * NH * 192 * 64))) return rc;
+        if ((rc = dev_alloc(h, &h->wo_bf16, sets * NH * 64 * 64))) return rc;
+        if (bf16_setup(h->bf, h->w1_bf16, h->wo_bf16, (int)sets) != 0)
+            return fail(h, SLIME_CA_ECUDA, "tensor-map / kernel attribute set-up failed: " + std::string(bf16_error()));
+    } else {
+        if ((rc = dev_alloc(h, &h->wpiv_f32, sets * NH * NC * 192))) return rc;
+        if ((rc = dev_alloc(h, &h->wo_f32, sets * NH * HD * NC))) return rc;
+    }
+    std::vector<float> ones((size_t)g.B * NC, 1.f);
+    CK(h, cudaMemcpy(h->scale, ones.data(), ones.size() * sizeof(float), cudaMemcpyHostToDevice));
+    return SLIME_CA_OK;
+}
+
+int slime_ca_destroy(slime_ca* h) {
+    if (!h) return SLIME_CA_EINVAL;
+    cudaSetDevice(h->cfg.device);
+    void* ptrs[] = {h->X, h->E, h->V, h->vprime[0], h->vprime[1], h->scale, h->mass, h->sums, h->partial, h->seg_sums,
+                    h->wpiv_f32, h->wo_f32, h->prm, h->w1_bf16, h->wo_bf16, h->gram_part, h->head_rank,
+                    h->pearson_part, h->fit_dev, h->dev_status};
+    for (void* p : ptrs)
+        if (p) cudaFree(p);
+    delete h;
+    return SLIME_CA_OK;
+}
+
+const char* slime_ca_last_error(const slime_ca* h) { return h ? h->err.c_str() : "null handle"; }
+size_t slime_ca_workspace_bytes(const slime_ca* h) { return h ? h->bytes : 0; }
+long long slime_ca_launch_count(const slime_ca* h) { return h ? h->launches : 0; }
+
+int slime_ca_set_weights(slime_ca* h, int set_index, const float* Wp, const float* Wi, const float* Wv,
+                         const float* Wo, const float* K, const float* mu, const float* sigma) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!Wp || !Wi || !Wv || !Wo || !K || !mu || !sigma) return fail(h, SLIME_CA_EINVAL, "null weight pointer");
+    if (set_index < 0 || set_index >= h->cfg.n_weight_sets) return fail(h, SLIME_CA_EINVAL, "weight set index out of range");
+    for (int i = 0; i < NH; ++i)
+        if (!(sigma[i] > 0.f)) return fail(h, SLIME_CA_EINVAL, "sigma must be positive");
+    CK(h, cudaSetDevice(h->cfg.device));
+    std::vector<float> prm((size_t)NH * PRM, 0.f);
+    for (int hd = 0; hd < NH; ++hd) {
+        for (int t = 0; t < 9; ++t) prm[hd * PRM + t] = K[hd * 9 + t];
+        prm[hd * PRM + 9] = mu[hd];
+        prm[hd * PRM + 10] = -1.f / (2.f * sigma[hd] * sigma[hd]);
+    }
+    CK(h, cudaMemcpy(h->prm + (size_t)set_index * NH * PRM, prm.data(), prm.size() * sizeof(float), cudaMemcpyHostToDevice));
+    if (is_bf16(h)) {
+        // B operands are stored "K-major": one row per output column, the 64 inputs contiguous.
+        std::vector<__nv_bfloat16> w1((size_t)NH * 192 * 64), wo((size_t)NH * 64 * 64);
+        for (int hd = 0; hd < NH; ++hd)
+            for (int c = 0; c < NC; ++c)
+                for (int d = 0; d < HD; ++d) {
+                    const size_t src = ((size_t)hd * NC + c) * HD + d;
+                    w1[((size_t)hd * 192 + d) * 64 + c] = __float2bfloat16(Wp[src]);
+                    w1[((size_t)hd * 192 + 64 + d) * 64 + c] = __float2bfloat16(Wi[src]);
+                    w1[((size_t)hd * 192 + 128 + d) * 64 + c] = __float2bfloat16(Wv[src]);
+                    // Wo[(hd*64+d)][c] -> row c (output channel), column d
+                    wo[((size_t)hd * 64 + c) * 64 + d] = __float2bfloat16(Wo[((size_t)hd * HD + d) * NC + c]);
+                }
+        CK(h, cudaMemcpy(h->w1_bf16 + (size_t)set_index * NH * 192 * 64, w1.data(), w1.size() * 2, cudaMemcpyHostToDevice));
+        CK(h, cudaMemcpy(h->wo_bf16 + (size_t)set_index * NH * 64 * 64, wo.data(), wo.size() * 2, cudaMemcpyHostToDevice));
+    } else {
+        std::vector<float> w((size_t)NH * NC * 192);
+        for (int hd = 0; hd < NH; ++hd)
+            for (int c = 0; c < NC; ++c)
+                for (int d = 0; d < HD; ++d) {
+                    const size_t src = ((size_t)hd * NC + c) * HD + d;
+                    const size_t dst = ((size_t)hd * NC + c) * 192 + d;
+                    w[dst] = Wp[src]; w[dst + 64] = Wi[src]; w[dst + 128] = Wv[src];
+                }
+        CK(h, cudaMemcpy(h->wpiv_f32 + (size_t)set_index * NH * NC * 192, w.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice));
+        CK(h, cudaMemcpy(h->wo_f32 + (size_t)set_index * NH * HD * NC, Wo, (size_t)NH * HD * NC * sizeof(float), cudaMemcpyHostToDevice));
+    }
+    h->weights_set[set_index] = 1;
+    return SLIME_CA_OK;
+}
+
+int slime_ca_set_state_device(slime_ca* h, const void* dev_state, int dtype, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!dev_state || (dtype != SLIME_CA_F32 && dtype != SLIME_CA_BF16)) return fail(h, SLIME_CA_EINVAL, "bad state pointer or dtype");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const Geom& g = h->g;
+    const size_t n = (size_t)g.B * g.H * g.W * NC;
+    const int blocks = grid_for(n);
+    if (is_bf16(h)) {
+        if (dtype == SLIME_CA_BF16) k_state_in<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)dev_state, (__nv_bfloat16*)h->X, g);
+        else k_state_in<float, __nv_bfloat16><<<blocks, 256, 0, st>>>((const float*)dev_state, (__nv_bfloat16*)h->X, g);
+    } else {
+        if (dtype == SLIME_CA_BF16) k_state_in<__nv_bfloat16, float><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)dev_state, (float*)h->X, g);
+        else k_state_in<float, float><<<blocks, 256, 0, st>>>((const float*)dev_state, (float*)h->X, g);
+    }
+    LAUNCHED(h);
+    int rc = channel_sums(h, 1, st);
+    if (rc) return rc;
+    h->state_set = true;
+    h->vp_steps = 0;
+    return SLIME_CA_OK;
+}
+
+int slime_ca_get_state_device(slime_ca* h, void* dev_state, int dtype, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!dev_state || (dtype != SLIME_CA_F32 && dtype != SLIME_CA_BF16)) return fail(h, SLIME_CA_EINVAL, "bad state pointer or dtype");
+    if (!h->state_set) return fail(h, SLIME_CA_ESTATE, "no state has been loaded");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const Geom& g = h->g;
+    const int blocks = grid_for((size_t)g.B * g.H * g.W * NC);
+    if (is_bf16(h)) {
+        if (dtype == SLIME_CA_BF16) k_state_out<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)h->X, h->scale, (__nv_bfloat16*)dev_state, g);
+        else k_state_out<__nv_bfloat16, float><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)h->X, h->scale, (float*)dev_state, g);
+    } else {
+        if (dtype == SLIME_CA_BF16) k_state_out<float, __nv_bfloat16><<<blocks, 256, 0, st>>>((const float*)h->X, h->scale, (__nv_bfloat16*)dev_state, g);
+        else k_state_out<float, float><<<blocks, 256, 0, st>>>((const float*)h->X, h->scale, (float*)dev_state, g);
+    }
+    LAUNCHED(h);
+    return SLIME_CA_OK;
+}
+
+// Host transfers stage through the E intermediate (always at least 8x the state), so no extra memory.
+int slime_ca_set_state(slime_ca* h, const void* host_state, int host_dtype, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!host_state || (host_dtype != SLIME_CA_F32 && host_dtype != SLIME_CA_BF16)) return fail(h, SLIME_CA_EINVAL, "bad state pointer or dtype");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t n = (size_t)h->g.B * h->g.H * h->g.W * NC;
+    CK(h, cudaMemcpyAsync(h->E, host_state, n * (host_dtype == SLIME_CA_BF16 ? 2 : 4), cudaMemcpyHostToDevice, st));
+    int rc = slime_ca_set_state_device(h, h->E, host_dtype, stream);
+    if (rc) return rc;
+    CK(h, cudaStreamSynchronize(st));
+    return SLIME_CA_OK;
+}
+
+int slime_ca_get_state(slime_ca* h, void* host_state, int host_dtype, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!host_state) return fail(h, SLIME_CA_EINVAL, "null state pointer");
+    int rc = slime_ca_get_state_device(h, h->E, host_dtype, stream);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t n = (size_t)h->g.B * h->g.H * h->g.W * NC;
+    CK(h, cudaMemcpyAsync(host_state, h->E, n * (host_dtype == SLIME_CA_BF16 ? 2 : 4), cudaMemcpyDeviceToHost, st));
+    CK(h, cudaStreamSynchronize(st));
+    return check_status_word(h);
+}
+
+int slime_ca_set_mass(slime_ca* h, const double* mass) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!mass) return fail(h, SLIME_CA_EINVAL, "null mass pointer");
+    CK(h, cudaSetDevice(h->cfg.device));
+    CK(h, cudaMemcpy(h->mass, mass, (size_t)h->g.B * NC * sizeof(double), cudaMemcpyHostToDevice));
+    return SLIME_CA_OK;
+}
+
+int slime_ca_get_mass(slime_ca* h, double* mass) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!mass) return fail(h, SLIME_CA_EINVAL, "null mass pointer");
+    CK(h, cudaSetDevice(h->cfg.device));
+    CK(h, cudaMemcpy(mass, h->mass, (size_t)h->g.B * NC * sizeof(double), cudaMemcpyDeviceToHost));
+    return SLIME_CA_OK;
+}
+
+int slime_ca_step_partial(slime_ca* h, void* stream) {
+    int rc = ready(h);
+    if (rc) return rc;
+    CK(h, cudaSetDevice(h->cfg.device));
+    void* emit = nullptr;
+    if (h->cfg.keep_vprime) { h->vp_last ^= 1; emit = h->vprime[h->vp_last]; ++h->vp_steps; }
+    rc = step_kernels(h, emit, (cudaStream_t)stream);
+    if (rc) return rc;
+    ++h->steps_done;
+    return SLIME_CA_OK;
+}
+
+int slime_ca_step_finish(slime_ca* h, void* stream) {
+    int rc = ready(h);
+    if (rc) return rc;
+    CK(h, cudaSetDevice(h->cfg.device));
+    const int n = h->g.B * NC;
+    k_scale_from_sums<<<(n + 255) / 256, 256, 0, (cudaStream_t)stream>>>(h->sums, h->mass, h->scale, n);
+    LAUNCHED(h);
+    return SLIME_CA_OK;
+}
+
+int slime_ca_step(slime_ca* h, int n_steps, void* stream) {
+    int rc = ready(h);
+    if (rc) return rc;
+    if (n_steps < 0) return fail(h, SLIME_CA_EINVAL, "negative step count");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const int n = h->g.B * NC;
+    for (int i = 0; i < n_steps; ++i) {
+        void* emit = nullptr;
+        if (h->cfg.keep_vprime && i >= n_steps - 2) { h->vp_last ^= 1; emit = h->vprime[h->vp_last]; ++h->vp_steps; }
+        rc = step_kernels(h, emit, st);
+        if (rc) return rc;
+        k_scale_from_sums<<<(n + 255) / 256, 256, 0, st>>>(h->sums, h->mass, h->scale, n);
+        LAUNCHED(h);
+        ++h->steps_done;
+    }
+    return SLIME_CA_OK;
+}
+
+int slime_ca_step_timed(slime_ca* h, int n_steps, void* stream, float* ms) {
+    int rc = ready(h);
+    if (rc) return rc;
+    if (n_steps <= 0 || n_steps > 4096 || !ms) return fail(h, SLIME_CA_EINVAL, "bad step count or null output");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    std::vector<cudaEvent_t> ev((size_t)n_steps * 4);
+    for (auto& e : ev) CK(h, cudaEventCreate(&e));
+    const int n = h->g.B * NC;
+    for (int i = 0; i < n_steps; ++i) {
+        rc = step_kernels(h, nullptr, st, &ev[(size_t)i * 4]);
+        if (rc) return rc;
+        k_scale_from_sums<<<(n + 255) / 256, 256, 0, st>>>(h->sums, h->mass, h->scale, n);
+        LAUNCHED(h);
+        CK(h, cudaEventRecord(ev[(size_t)i * 4 + 3], st));
+        ++h->steps_done;
+    }
+    CK(h, cudaStreamSynchronize(st));
+    ms[0] = ms[1] = ms[2] = 0.f;
+    for (int i = 0; i < n_steps; ++i)
+        for (int k = 0; k < 3; ++k) {
+            float t = 0.f;
+            CK(h, cudaEventElapsedTime(&t, ev[(size_t)i * 4 + k], ev[(size_t)i * 4 + k + 1]));
+            ms[k] += t;
+        }
+    for (auto& e : ev) cudaEventDestroy(e);
+    return check_status_word(h);
+}
+
+int slime_ca_buffer(slime_ca* h, int which, void** dev_ptr, size_t* bytes) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!dev_ptr || !bytes) return fail(h, SLIME_CA_EINVAL, "null output pointer");
+    const Geom& g = h->g;
+    const size_t vn = (size_t)g.B * NH * g.H * g.W * HD * h->esz;
+    switch (which) {
+        case SLIME_CA_BUF_STATE: *dev_ptr = h->X; *bytes = (size_t)g.B * g.state_rows() * g.W * NC * h->esz; break;
+        case SLIME_CA_BUF_SCALE: *dev_ptr = h->scale; *bytes = (size_t)g.B * NC * sizeof(float); break;
+        case SLIME_CA_BUF_MASS: *dev_ptr = h->mass; *bytes = (size_t)g.B * NC * sizeof(double); break;
+        case SLIME_CA_BUF_SUMS: *dev_ptr = h->sums; *bytes = (size_t)g.B * NC * sizeof(double); break;
+        case SLIME_CA_BUF_VPRIME_PREV: *dev_ptr = h->vprime[h->vp_last ^ 1]; *bytes = h->vprime[0] ? vn : 0; break;
+        case SLIME_CA_BUF_VPRIME_LAST: *dev_ptr = h->vprime[h->vp_last]; *bytes = h->vprime[0] ? vn : 0; break;
+        default: return fail(h, SLIME_CA_EINVAL, "unknown buffer id");
+    }
+    return SLIME_CA_OK;
+}
+
+int slime_ca_fitness(slime_ca* h, float* rank, float* coherence, float* fitness, float* hunger, void* stream) {
+    int rc = ready(h);
+    if (rc) return rc;
+    if (!h->cfg.keep_vprime) return fail(h, SLIME_CA_ESTATE, "handle was created without keep_vprime");
+    if (h->vp_steps < 2) return fail(h, SLIME_CA_ESTATE, "fitness needs two steps since the state was loaded");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const Geom& g = h->g;
+    const int cells = g.H * g.W;
+    const void* va = h->vprime[h->vp_last ^ 1];
+    const void* vb = h->vprime[h->vp_last];
+    const size_t per_grid = (size_t)cells * HC;
+    if (is_bf16(h)) {
+        k_gram<__nv_bfloat16><<<dim3(h->gram_splits, NH, g.B), 256, 0, st>>>((const __nv_bfloat16*)vb, cells, h->gram_part);
+        LAUNCHED(h);
+        k_pearson<__nv_bfloat16><<<dim3(h->pearson_splits, g.B), 256, 0, st>>>((const __nv_bfloat16*)va, (const __nv_bfloat16*)vb, per_grid, h->pearson_part);
+        LAUNCHED(h);
+    } else {
+        k_gram<float><<<dim3(h->gram_splits, NH, g.B), 256, 0, st>>>((const float*)vb, cells, h->gram_part);
+        LAUNCHED(h);
+        k_pearson<float><<<dim3(h->pearson_splits, g.B), 256, 0, st>>>((const float*)va, (const float*)vb, per_grid, h->pearson_part);
+        LAUNCHED(h);
+    }
+    k_jacobi_rank<<<g.B * NH, 32, 0, st>>>(h->gram_part, h->gram_splits, h->head_rank);
+    LAUNCHED(h);
+    k_fitness_final<<<(g.B + 127) / 128, 128, 0, st>>>(h->head_rank, h->pearson_part, h->pearson_splits, (double)per_grid, h->fit_dev, g.B);
+    LAUNCHED(h);
+    std::vector<float> out((size_t)g.B * 4);
+    CK(h, cudaMemcpyAsync(out.data(), h->fit_dev, out.size() * sizeof(float), cudaMemcpyDeviceToHost, st));
+    CK(h, cudaStreamSynchronize(st));
+    for (int b = 0; b < g.B; ++b) {
+        if (rank) rank[b] = out[b * 4 + 0];
+        if (coherence) coherence[b] = out[b * 4 + 1];
+        if (fitness) fitness[b] = out[b * 4 + 2];
+        if (hunger) hunger[b] = out[b * 4 + 3];
+    }
+    return check_status_word(h);
+}
+
+int slime_ca_lift_images(slime_ca* h, const float* host_img, int img_h, int img_w, const float* host_L, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!host_img || !host_L || img_h <= 0 || img_w <= 0 || img_h > h->g.H || img_w > h->g.W)
+        return fail(h, SLIME_CA_EINVAL, "bad image pointer or image larger than the grid");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const Geom& g = h->g;
+    const size_t n_img = (size_t)g.B * img_h * img_w;
+    float* d_img = (float*)h->E;
+    float* d_L = (float*)h->V;
+    CK(h, cudaMemcpyAsync(d_img, host_img, n_img * sizeof(float), cudaMemcpyHostToDevice, st));
+    CK(h, cudaMemcpyAsync(d_L, host_L, NC * sizeof(float), cudaMemcpyHostToDevice, st));
+    const int blocks = grid_for((size_t)g.B * g.H * g.W * NC);
+    if (is_bf16(h)) k_lift<__nv_bfloat16><<<blocks, 256, 0, st>>>(d_img, img_h, img_w, d_L, (__nv_bfloat16*)h->X, g);
+    else k_lift<float><<<blocks, 256, 0, st>>>(d_img, img_h, img_w, d_L, (float*)h->X, g);
+    LAUNCHED(h);
+    int rc = channel_sums(h, 1, st);
+    if (rc) return rc;
+    CK(h, cudaStreamSynchronize(st));
+    h->state_set = true;
+    h->vp_steps = 0;
+    return SLIME_CA_OK;
+}
+
+int slime_ca_pool_readout(slime_ca* h, const float* host_Wr, const float* host_br, int n_out, float* host_logits, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!host_Wr || !host_logits || n_out <= 0 || n_out > 1024) return fail(h, SLIME_CA_EINVAL, "bad readout arguments");
+    if (!h->state_set) return fail(h, SLIME_CA_ESTATE, "no state has been loaded");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const Geom& g = h->g;
+    int rc = channel_sums(h, 0, st);   // sums of what is stored now; mass and scale untouched
+    if (rc) return rc;
+    float* d_W = (float*)h->E;
+    float* d_b = d_W + (size_t)NC * n_out;
+    float* d_out = d_b + n_out;
+    CK(h, cudaMemcpyAsync(d_W, host_Wr, (size_t)NC * n_out * sizeof(float), cudaMemcpyHostToDevice, st));
+    if (host_br) CK(h, cudaMemcpyAsync(d_b, host_br, n_out * sizeof(float), cudaMemcpyHostToDevice, st));
+    k_pool_readout<<<g.B, ((n_out + 31) / 32) * 32, 0, st>>>(h->sums, h->scale, 1.0 / ((double)g.H * g.W), d_W, host_br ? d_b : nullptr, n_out, d_out);
+    LAUNCHED(h);
+    CK(h, cudaMemcpyAsync(host_logits, d_out, (size_t)g.B * n_out * sizeof(float), cudaMemcpyDeviceToHost, st));
+    CK(h, cudaStreamSynchronize(st));
+    return SLIME_CA_OK;
+}
+
+void launch_multi_head_ca(float* ca_state, float* weights, float* ca_output, int batch_size, int grid_size) {
+    static slime_ca* cached = nullptr;
+    if (!ca_state || !weights || !ca_output || batch_size <= 0 || grid_size <= 0) {
+        fprintf(stderr, "launch_multi_head_ca: bad arguments\n");
+        return;
+    }
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cached && (cached->cfg.batch != batch_size || cached->cfg.height != grid_size || cached->cfg.device != dev)) {
+        slime_ca_destroy(cached);
+        cached = nullptr;
+    }
+    if (!cached) {
+        slime_ca_config cfg{batch_size, grid_size, grid_size, 1, SLIME_CA_F32, 0.1f, dev, 0, 1};
+        if (slime_ca_create(&cfg, &cached) != SLIME_CA_OK) {
+            fprintf(stderr, "launch_multi_head_ca: %s\n", slime_ca_last_error(cached));
+            if (cached) slime_ca_destroy(cached);
+            cached = nullptr;
+            return;
+        }
+    }
+    const size_t wn = (size_t)NH * NC * HD;
+    std::vector<float> w(3 * wn), wo((size_t)HC * NC, 0.f), k(NH * 9, 1.f / 9.f), mu(NH, 0.2f), sg(NH, 0.03f);
+    if (cudaMemcpy(w.data(), weights, w.size() * sizeof(float), cudaMemcpyDeviceToHost) != cudaSuccess ||
+        slime_ca_set_weights(cached, 0, w.data(), w.data() + wn, w.data() + 2 * wn, wo.data(), k.data(), mu.data(), sg.data()) ||
+        slime_ca_set_state_device(cached, ca_state, SLIME_CA_F32, nullptr) || slime_ca_step(cached, 1, nullptr)) {
+        fprintf(stderr, "launch_multi_head_ca: %s\n", slime_ca_last_error(cached));
+        return;
+    }
+    void* vp = nullptr;
+    size_t bytes = 0;
+    slime_ca_buffer(cached, SLIME_CA_BUF_VPRIME_LAST, &vp, &bytes);
+    if (cudaMemcpy(ca_output, vp, bytes, cudaMemcpyDeviceToDevice) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess)
+        fprintf(stderr, "launch_multi_head_ca: %s\n", cudaGetErrorString(cudaGetLastError()));
+}
+
+}  // extern "C"
