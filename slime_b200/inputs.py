@@ -132,8 +132,12 @@ def make_images(batch: int, size: int = 28, seed: int = 42, first: int = 0) -> n
 
 
 def make_lift_readout(seed: int = 42, n_out: int = 10):
-    """Lift vector L[64] ~ N(0,1), readout Wr[64,n_out] ~ N(0,1/64), bias br[n_out] ~ N(0,1)/10."""
-    L = normal(seed, _S_LIFT, CHANNELS).astype(np.float32)
+    """Lift vector L[64] = 0.5 + |N(0,1)|/2, readout Wr[64,n_out] ~ N(0,1/64), bias br[n_out] ~ N(0,1)/10.
+
+    The lift is kept positive: the step renormalises every channel to its initial mass, which is ill-posed
+    (and diverges within a few steps) for a channel whose mass is near zero or of mixed sign.
+    """
+    L = (0.5 + 0.5 * np.abs(normal(seed, _S_LIFT, CHANNELS))).astype(np.float32)
     Wr = (normal(seed, _S_READ_W, CHANNELS * n_out) / 8.0).astype(np.float32).reshape(CHANNELS, n_out)
     br = (normal(seed, _S_READ_B, n_out) / 10.0).astype(np.float32)
     return L, Wr, br
