@@ -211,7 +211,15 @@ def main():
     ms_e2e = timed(e2e_step, args.steps)
     e2e = {"value": world * cells * S * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
            "h2d_bytes_per_step": state_bytes, "d2h_bytes_per_step": state_bytes}
-    finite = bool(torch.isfinite(host_out.float()).all())
+    # The specified generators make the step's zero-mean component grow about 1.3x per step (the oracle shows the
+    # same), so fp32 overflows between step 40 and 48; record how far the trajectory stays finite.
+    finite_after = {}
+    with capi.Handle(1, GRID, GRID, dtype=dt_code, device=local) as h1:
+        h1.set_weights(inputs.make_weight_sets(1, seed=42))
+        h1.set_state(X0[:1])
+        for k in (16, 32, 48, 64):
+            h1.step(16, stream)
+            finite_after[str(k)] = bool(np.isfinite(h1.get_state(stream)).all())
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -223,7 +231,7 @@ def main():
                                  (2 * cells * 512 * (2 if args.dtype == "bf16" else 4) / 1e9),
                            "parallelism": f"batch-sharded x{world}, no data-path collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
-                "outputs_finite": finite}
+                "state_finite_after_steps": finite_after}
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(ca_steps_sample=4, grids=2)
         print(json.dumps(line), flush=True)
