@@ -1,15 +1,23 @@
 // bf16 path of the CA step: bf16 storage of state, weights and intermediates, fp32 accumulation and stencil
-// math, projections on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, weight tiles
+// math, projections on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operand tiles
 // fetched by TMA).  Same two-kernel split as the fp32 path (ca_f32.cuh):
 //
 //   k1_bf16  per 8x16-cell tile (128 cells = UMMA M): state halo tile -> per head the 3x3-convolved input as a
 //            swizzled K-major A operand; U = conv_h(X) Wp_h (N=64) and I|V = X [Wi_h|Wv_h] (N=128) into 192
-//            TMEM columns; epilogue: growth bell, E = exp(G*I), write E and V (bf16, per-head planar).
-//   k2_bf16  per tile and head: E (2-cell halo) and V (1-cell halo) by cp.async; separable box sums marching
-//            down columns: R = V / box3(E), V' = E * box3(R); V' is the A operand of Y += V'_h Wo_h (N=64)
-//            accumulated in TMEM over the 8 heads; epilogue: X+ = scale*X + dt*Y (bf16), per-tile channel sums.
+//            TMEM columns; epilogue: growth bell, E = exp(G*I), write E and V (bf16, per-head planes).
+//   k2_bf16  persistent, warp-specialised, one CTA per SM.  A producer warp streams (tile, head) items - the E
+//            tile with a 2-cell halo, the V tile with a 1-cell halo and the head's Wo slice - through a 3-stage
+//            TMA ring; two groups of 9 compute warps take alternate heads: separable box sums marching down
+//            columns in packed fp32 (R = V / box3(E) in place, V' = E * box3(R)), V' written as a swizzled A
+//            operand; an MMA warp issues Y += V'_h Wo_h (N=64) into a double-buffered TMEM accumulator in head
+//            order; the epilogue X+ = scale*X + dt*Y (bf16, in place) and the tile's channel sums run one tile
+//            behind.
 //
-// Shared-memory operand tiles are [rows][128 B] with the 128-byte swizzle: the 16-byte chunk q of row m
+// E/V planes are [B][8][H+4][W+4][64] with a 2-cell apron all around: k1 writes every cell it computes to its
+// own position and to every apron position that wraps onto it, so k2 never wraps or clamps and each of its
+// tiles is one TMA box (boxes hanging over the far edge are zero-filled and only feed cells that are masked).
+//
+// Shared-memory UMMA operand tiles are [rows][128 B] with the 128-byte swizzle: the 16-byte chunk q of row m
 // lives at m*128 + ((q ^ (m & 7)) << 4), tile bases 1024-byte aligned.
 #pragma once
 #include <cuda.h>
@@ -20,14 +28,16 @@
 namespace slime {
 
 constexpr int TBH = 8, TBW = 16;      // tile: 8 rows x 16 columns = 128 cells
+constexpr int APRON = 2;              // apron of the E/V planes, cells
 constexpr int K1B_THREADS = 256;
-constexpr int K2B_THREADS = 288;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct Bf16Plan {
-    int tiles_x = 1, k1_tiles = 1, k2_tiles = 1;
+    int tiles_x = 1, k1_tiles = 1, k2_tiles = 1, k2_grid = 1;
     CUtensorMap map_w1;   // [sets*8*192][64] bf16, box 64 x 192, 128B swizzle
     CUtensorMap map_wo;   // [sets*8*64][64]  bf16, box 64 x 64,  128B swizzle
+    CUtensorMap map_e;    // E planes [B*8][H+4][W+4][64], box 64 x 20 x 12 x 1
+    CUtensorMap map_v;    // V planes, box 64 x 18 x 10 x 1
 };
 
 // ---- shared-memory maps (byte offsets from a 1024-aligned base) -------------------------------------------
@@ -40,13 +50,21 @@ constexpr int SMEM = BYTES + 1024;    // slack for manual 1024-byte alignment
 constexpr uint32_t TMEM_COLS = 256;
 }  // namespace k1b
 namespace k2b {
-constexpr int A_VP = 0, WO0 = 16384, WO_STAGE = 8192, ES = WO0 + 2 * WO_STAGE;   // 32768
-constexpr int ES_BYTES = 12 * 20 * 128, VS = ES + ES_BYTES, VS_BYTES = 10 * 18 * 128;
-constexpr int SCALE = VS + VS_BYTES, BARS = SCALE + 256, TMEM_PTR = BARS + 32;
+constexpr int STAGES = 3;
+constexpr int WO_OFF = 0, E_OFF = 8192, E_BYTES = 12 * 20 * 128, V_OFF = E_OFF + E_BYTES, V_BYTES = 10 * 18 * 128;
+constexpr uint32_t STAGE_TX = 8192 + E_BYTES + V_BYTES;                 // 61952 bytes land per item
+constexpr int STAGE_BYTES = 62464;                                      // rounded up to a multiple of 1024
+constexpr int A_VP = STAGES * STAGE_BYTES;                              // two 16 KB operand tiles, one per group
+constexpr int RED = A_VP + 2 * 16384;                                   // [2 groups][4 quads][64] fp32
+constexpr int BARS = RED + 2 * 4 * 64 * 4;
+constexpr int TMEM_PTR = BARS + 20 * 8;
 constexpr int BYTES = TMEM_PTR + 16;
 constexpr int SMEM = BYTES + 1024;
-constexpr uint32_t TMEM_COLS = 64;
-static_assert(ES_BYTES + VS_BYTES >= 128 * 64 * 4, "the channel-sum scratch aliases the E and V tiles");
+constexpr uint32_t TMEM_COLS = 128;                                     // two 64-column accumulators
+constexpr int GROUP = 288;                                              // compute threads per group (9 warps)
+constexpr int THREADS = 2 * GROUP + 64;                                 // + TMA warp + MMA warp
+static_assert(STAGE_TX <= STAGE_BYTES && STAGE_BYTES % 1024 == 0, "stage layout");
+static_assert(SMEM <= 227 * 1024, "k2 shared memory");
 }  // namespace k2b
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
@@ -55,6 +73,12 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
 }
 __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
     return make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+}
+__device__ __forceinline__ void unpack8p(const uint4& v, ptx::f2 (&f)[4]) {
+    f[0] = ptx::bf16x2_to_f2(v.x); f[1] = ptx::bf16x2_to_f2(v.y); f[2] = ptx::bf16x2_to_f2(v.z); f[3] = ptx::bf16x2_to_f2(v.w);
+}
+__device__ __forceinline__ uint4 pack8p(const ptx::f2 (&f)[4]) {
+    return make_uint4(ptx::f2_to_bf16x2(f[0]), ptx::f2_to_bf16x2(f[1]), ptx::f2_to_bf16x2(f[2]), ptx::f2_to_bf16x2(f[3]));
 }
 __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
     return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~uintptr_t(1023));
@@ -83,7 +107,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __nv_bfloat16* __restr
     const int ty0 = (blockIdx.x / g.tiles_x) * TBH - g.he;
     const int set = b / g.per_set;
     const size_t xplane = (size_t)g.state_rows() * g.W * NC;
-    const size_t eplane = (size_t)g.ev_rows() * g.W * HD;
+    const size_t eplane = (size_t)g.ev_h * g.ev_w * HD;
 
     if (tid == 0) {
         ptx::mbar_init(&full[0], 1);
@@ -132,6 +156,20 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __nv_bfloat16* __restr
     const int r_ep = ty0 + (m_ep >> 4), x_ep = tx0 + (m_ep & 15);
     const bool valid_ep = r_ep < g.H + g.he && x_ep < g.W;
     const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
+
+    // Where this thread's cell goes inside a plane: its own position and the apron positions that wrap onto it.
+    // Grids narrower or shorter than twice the apron can wrap more than once; they take the general loop below.
+    const bool tiny = g.W < 2 * APRON || (g.wrap_y && g.H < 2 * APRON);
+    const size_t own_off = ((size_t)(r_ep + APRON) * g.ev_w + x_ep + APRON) * HD;
+    size_t dup_off[3];
+    int ndup = 0;
+    if (valid_ep && !tiny) {
+        const int xd = x_ep < APRON ? x_ep + g.W : (x_ep >= g.W - APRON ? x_ep - g.W : -100);
+        const int rd = !g.wrap_y ? -100 : (r_ep < APRON ? r_ep + g.H : (r_ep >= g.H - APRON ? r_ep - g.H : -100));
+        if (xd != -100) dup_off[ndup++] = ((size_t)(r_ep + APRON) * g.ev_w + xd + APRON) * HD;
+        if (rd != -100) dup_off[ndup++] = ((size_t)(rd + APRON) * g.ev_w + x_ep + APRON) * HD;
+        if (xd != -100 && rd != -100) dup_off[ndup++] = ((size_t)(rd + APRON) * g.ev_w + xd + APRON) * HD;
+    }
 
     for (int h = 0; h < NH; ++h) {
         // ---- 3x3 stencil of head h on the state tile -> A operand ------------------------------------------
@@ -182,7 +220,8 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __nv_bfloat16* __restr
 
         // ---- epilogue: growth bell, activation, E = exp(A); E and V to global ---------------------------------
         const float mu = prm_s[h * PRM + 9], nisl2 = prm_s[h * PRM + 10] * LOG2E;
-        const size_t obase = ((size_t)b * NH + h) * eplane + ((size_t)g.erow(r_ep) * g.W + (valid_ep ? x_ep : 0)) * HD;
+        __nv_bfloat16* Eh = E + ((size_t)b * NH + h) * eplane;
+        __nv_bfloat16* Vh = V + ((size_t)b * NH + h) * eplane;
 #pragma unroll
         for (int sub = 0; sub < 2; ++sub) {
             const int c0 = half * 32 + sub * 16;
@@ -205,13 +244,30 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __nv_bfloat16* __restr
                 pe[j] = pack_bf16(e2[0], e2[1]);
                 pv[j] = pack_bf16(__uint_as_float(rv[2 * j]), __uint_as_float(rv[2 * j + 1]));
             }
+            const uint4 e_lo = make_uint4(pe[0], pe[1], pe[2], pe[3]), e_hi = make_uint4(pe[4], pe[5], pe[6], pe[7]);
+            const uint4 v_lo = make_uint4(pv[0], pv[1], pv[2], pv[3]), v_hi = make_uint4(pv[4], pv[5], pv[6], pv[7]);
             if (valid_ep) {
-                uint4* pE = reinterpret_cast<uint4*>(E + obase + c0);
-                uint4* pV = reinterpret_cast<uint4*>(V + obase + c0);
-                pE[0] = make_uint4(pe[0], pe[1], pe[2], pe[3]);
-                pE[1] = make_uint4(pe[4], pe[5], pe[6], pe[7]);
-                pV[0] = make_uint4(pv[0], pv[1], pv[2], pv[3]);
-                pV[1] = make_uint4(pv[4], pv[5], pv[6], pv[7]);
+                if (!tiny) {
+#pragma unroll
+                    for (int d = 0; d < 4; ++d) {
+                        if (d > ndup) break;
+                        const size_t off = (d == 0 ? own_off : dup_off[d - 1]) + c0;
+                        uint4* pE = reinterpret_cast<uint4*>(Eh + off);
+                        uint4* pV = reinterpret_cast<uint4*>(Vh + off);
+                        pE[0] = e_lo; pE[1] = e_hi; pV[0] = v_lo; pV[1] = v_hi;
+                    }
+                } else {
+                    for (int ky = -2 * APRON; ky <= 2 * APRON; ++ky)
+                        for (int kx = -2 * APRON; kx <= 2 * APRON; ++kx) {
+                            if (ky != 0 && !g.wrap_y) continue;
+                            const int rr = r_ep + ky * g.H, xx = x_ep + kx * g.W;
+                            if (rr < -APRON || rr >= g.H + APRON || xx < -APRON || xx >= g.W + APRON) continue;
+                            const size_t off = ((size_t)(rr + APRON) * g.ev_w + xx + APRON) * HD + c0;
+                            uint4* pE = reinterpret_cast<uint4*>(Eh + off);
+                            uint4* pV = reinterpret_cast<uint4*>(Vh + off);
+                            pE[0] = e_lo; pE[1] = e_hi; pV[0] = v_lo; pV[1] = v_hi;
+                        }
+                }
             }
         }
         ptx::tc_fence_before();
@@ -221,194 +277,266 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __nv_bfloat16* __restr
 }
 
 // =============================================================================================================
-__global__ void __launch_bounds__(K2B_THREADS, 2)
-k2_bf16(const __grid_constant__ CUtensorMap map_wo, __nv_bfloat16* __restrict__ X, const float* __restrict__ scale,
-        const __nv_bfloat16* __restrict__ E, const __nv_bfloat16* __restrict__ V, float* __restrict__ partial,
-        __nv_bfloat16* __restrict__ vprime, int* __restrict__ status, Geom g) {
+// k2: the tile a CTA-local tile index refers to
+struct K2Tile {
+    int b, ty0, tx0, index;
+};
+__device__ __forceinline__ K2Tile k2_tile(int t, int tiles_per_grid, int tiles_x) {
+    K2Tile r;
+    r.index = t;
+    r.b = t / tiles_per_grid;
+    const int tt = t - r.b * tiles_per_grid;
+    r.ty0 = (tt / tiles_x) * TBH;
+    r.tx0 = (tt % tiles_x) * TBW;
+    return r;
+}
+
+// Epilogue of one finished tile, run by 8 warps (256 threads) of one compute group: X+ = scale*X + dt*Y in
+// place, and the tile's per-channel sums of the stored (rounded) values -> partial[tile][64].
+__device__ __forceinline__ void k2_epilogue(const K2Tile& t, uint32_t acc_taddr, __nv_bfloat16* __restrict__ X,
+                                            const float* __restrict__ scale, float* __restrict__ partial,
+                                            float* red, int bar_id, int gt, int cta_warp, const Geom& g) {
+    const int lane = gt & 31, quad = cta_warp & 3, half = (gt >> 5) >> 2;
+    const int m = quad * 32 + lane;
+    const int r = t.ty0 + (m >> 4), x = t.tx0 + (m & 15);
+    const bool valid = r < g.H && x < g.W;
+    const size_t xplane = (size_t)g.state_rows() * g.W * NC;
+    __nv_bfloat16* px = X + (size_t)t.b * xplane + ((size_t)g.xrow(valid ? r : 0) * g.W + (valid ? x : 0)) * NC;
+    const float* sc = scale + t.b * NC;
+#pragma unroll
+    for (int sub = 0; sub < 2; ++sub) {
+        const int c0 = half * 32 + sub * 16;
+        uint32_t ry[16];
+        ptx::tmem_ld16(acc_taddr + ((uint32_t)(quad * 32) << 16) + c0, ry);
+        ptx::tmem_ld_wait();
+        float xo[16];
+        if (valid) {
+            float f0[8], f1[8];
+            unpack8(*reinterpret_cast<const uint4*>(px + c0), f0);
+            unpack8(*reinterpret_cast<const uint4*>(px + c0 + 8), f1);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                xo[k] = fmaf(g.dt, __uint_as_float(ry[k]), f0[k] * __ldg(sc + c0 + k));
+                xo[8 + k] = fmaf(g.dt, __uint_as_float(ry[8 + k]), f1[k] * __ldg(sc + c0 + 8 + k));
+            }
+            uint32_t pk[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                pk[k] = pack_bf16(xo[2 * k], xo[2 * k + 1]);
+                xo[2 * k] = bf16_lo(pk[k]);          // sum what is stored, after rounding
+                xo[2 * k + 1] = bf16_hi(pk[k]);
+            }
+            *reinterpret_cast<uint4*>(px + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(px + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        } else {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) xo[k] = 0.f;
+        }
+        // sum over the 32 cells of this warp, fixed tree: each step halves the channels a lane carries
+#pragma unroll
+        for (int w = 8; w >= 1; w >>= 1) {
+            const bool up = (lane & (w * 2)) != 0;
+#pragma unroll
+            for (int j = 0; j < w; ++j) {
+                const float send = up ? xo[j] : xo[j + w];
+                const float keep = up ? xo[j + w] : xo[j];
+                xo[j] = keep + __shfl_xor_sync(0xffffffffu, send, w * 2);
+            }
+        }
+        xo[0] += __shfl_xor_sync(0xffffffffu, xo[0], 1);
+        if ((lane & 1) == 0) {
+            const int ch = ((lane >> 4) & 1) * 8 + ((lane >> 3) & 1) * 4 + ((lane >> 2) & 1) * 2 + ((lane >> 1) & 1);
+            red[quad * 64 + c0 + ch] = xo[0];
+        }
+    }
+    ptx::bar_sync(bar_id, 256);
+    if (gt < NC) partial[(size_t)t.index * NC + gt] = (red[gt] + red[64 + gt]) + (red[128 + gt] + red[192 + gt]);
+}
+
+__global__ void __launch_bounds__(k2b::THREADS, 1)
+k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUtensorMap map_e,
+        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ X, const float* __restrict__ scale,
+        float* __restrict__ partial, __nv_bfloat16* __restrict__ vprime, int* __restrict__ status, int n_tiles,
+        int tiles_per_grid, Geom g) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = align1024(smem_raw);
-    uint8_t* a_vp = sm + k2b::A_VP;
-    uint8_t* es = sm + k2b::ES;       // [12][20] cells x 128 B
-    uint8_t* vs = sm + k2b::VS;       // [10][18] cells x 128 B: V, then R in place
-    float* red = reinterpret_cast<float*>(es);   // [128][64] fp32 after the last head
-    float* scale_s = reinterpret_cast<float*>(sm + k2b::SCALE);
-    uint64_t* full = reinterpret_cast<uint64_t*>(sm + k2b::BARS);
-    uint64_t* mma_bar = full + 2;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + k2b::BARS);
+    // Every barrier has exactly one waiting party that observes each of its phases in turn (a parity wait can
+    // not tell a phase from the one two earlier).  Items alternate between the two compute groups and between
+    // three stages, so "TMA landed" is kept per (group, stage): item i uses full[(i & 1) * 3 + i % 3], phase i / 6.
+    uint64_t* full = bars;              // [2][3] TMA landed in stage s for group g
+    uint64_t* empty = bars + 6;         // [3]  the UMMA of the item in stage s is done (Wo read; E/V long since)
+    uint64_t* vp_full = bars + 9;       // [2]  group g's operand tile is written
+    uint64_t* vp_empty = bars + 11;     // [2]  the UMMA reading group g's operand tile is done
+    uint64_t* acc_full = bars + 13;     // [2]  all 8 heads of a tile are accumulated
+    uint64_t* acc_empty = bars + 15;    // [2]  the epilogue has drained the accumulator
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(sm + k2b::TMEM_PTR);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.y;
-    const int tx0 = (blockIdx.x % g.tiles_x) * TBW;
-    const int ty0 = (blockIdx.x / g.tiles_x) * TBH;
-    const int set = b / g.per_set;
-    const size_t xplane = (size_t)g.state_rows() * g.W * NC;
-    const size_t eplane = (size_t)g.ev_rows() * g.W * HD;
-    const size_t vplane = (size_t)g.H * g.W * HD;
-
     if (tid == 0) {
-        ptx::mbar_init(&full[0], 1);
-        ptx::mbar_init(&full[1], 1);
-        ptx::mbar_init(mma_bar, 1);
+        for (int i = 0; i < 6; ++i) ptx::mbar_init(&full[i], 1);
+        for (int i = 0; i < 3; ++i) ptx::mbar_init(&empty[i], 1);
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&vp_full[i], 1); ptx::mbar_init(&vp_empty[i], 1);
+            ptx::mbar_init(&acc_full[i], 1); ptx::mbar_init(&acc_empty[i], 256);
+        }
         ptx::fence_barrier_init();
-        ptx::prefetch_tmap(&map_wo);
+        ptx::prefetch_tmap(&map_wo); ptx::prefetch_tmap(&map_e); ptx::prefetch_tmap(&map_v);
     }
     if (warp == 0) ptx::tmem_alloc(tmem_ptr, k2b::TMEM_COLS);
-    if (tid < NC) scale_s[tid] = scale[b * NC + tid];
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_ptr;
+    const int my_tiles = n_tiles > (int)blockIdx.x ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
-    if (tid == 0) {
-        for (int s = 0; s < 2; ++s) {
-            ptx::mbar_expect_tx(&full[s], k2b::WO_STAGE);
-            ptx::tma_load_2d(sm + k2b::WO0 + s * k2b::WO_STAGE, &map_wo, 0, (set * NH + s) * 64, &full[s]);
-        }
-    }
-    const uint32_t idesc = ptx::umma_idesc_bf16(128, 64);
-
-    for (int h = 0; h < NH; ++h) {
-        const __nv_bfloat16* Eh = E + ((size_t)b * NH + h) * eplane;
-        const __nv_bfloat16* Vh = V + ((size_t)b * NH + h) * eplane;
-        for (int i = tid; i < 240 * 8; i += K2B_THREADS) {
-            const int q = i & 7, cell = i >> 3;
-            const int r = ty0 + cell / 20 - 2, x = g.wrap_x(tx0 + cell % 20 - 2);
-            ptx::cp_async16(es + cell * 128 + q * 16, Eh + ((size_t)g.erow(r) * g.W + x) * HD + q * 8);
-        }
-        for (int i = tid; i < 180 * 8; i += K2B_THREADS) {
-            const int q = i & 7, cell = i >> 3;
-            const int r = ty0 + cell / 18 - 1, x = g.wrap_x(tx0 + cell % 18 - 1);
-            ptx::cp_async16(vs + cell * 128 + q * 16, Vh + ((size_t)g.erow(r) * g.W + x) * HD + q * 8);
-        }
-        ptx::cp_async_commit();
-        ptx::cp_async_wait<0>();
-        __syncthreads();
-
-        // ---- R = V / box3(E) on the 10 x 18 ring-extended tile: 18 columns x 8 chunks x 2 row segments ------
-        {
-            const int q = tid & 7, c = (tid >> 3) % 18, r0 = (tid / 144) * 5;
-            float hp2[8], hp1[8];
-#pragma unroll
-            for (int j = 0; j < 7; ++j) {
-                const uint8_t* row = es + ((r0 + j) * 20 + c) * 128 + q * 16;
-                float e0[8], e1[8], e2[8], hs[8];
-                unpack8(*reinterpret_cast<const uint4*>(row), e0);
-                unpack8(*reinterpret_cast<const uint4*>(row + 128), e1);
-                unpack8(*reinterpret_cast<const uint4*>(row + 256), e2);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) hs[k] = (e0[k] + e1[k]) + e2[k];
-                if (j >= 2) {
-                    uint4* pv = reinterpret_cast<uint4*>(vs + ((r0 + j - 2) * 18 + c) * 128 + q * 16);
-                    float v[8];
-                    unpack8(*pv, v);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) v[k] *= ptx::rcp((hp2[k] + hp1[k]) + hs[k]);
-                    *pv = pack8(v);
+    if (warp == 18) {
+        // ================= TMA producer ===================================================================
+        if (lane == 0) {
+            for (int k = 0; k < my_tiles; ++k) {
+                const K2Tile t = k2_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x);
+                const int set = t.b / g.per_set;
+                for (int h = 0; h < NH; ++h) {
+                    const int i = k * NH + h, s = i % 3, u = i / 3;
+                    ptx::mbar_wait(&empty[s], (u & 1) ^ 1, status, 210);
+                    uint8_t* st = sm + s * k2b::STAGE_BYTES;
+                    uint64_t* fb = &full[(h & 1) * 3 + s];
+                    ptx::mbar_expect_tx(fb, k2b::STAGE_TX);
+                    ptx::tma_load_2d(st + k2b::WO_OFF, &map_wo, 0, (set * NH + h) * 64, fb);
+                    ptx::tma_load_4d(st + k2b::E_OFF, &map_e, 0, t.tx0, t.ty0, t.b * NH + h, fb);
+                    ptx::tma_load_4d(st + k2b::V_OFF, &map_v, 0, t.tx0 + 1, t.ty0 + 1, t.b * NH + h, fb);
                 }
-#pragma unroll
-                for (int k = 0; k < 8; ++k) { hp2[k] = hp1[k]; hp1[k] = hs[k]; }
             }
         }
-        __syncthreads();
-        if (h > 0) {            // the previous head's UMMA must be done reading a_vp and its Wo stage
-            ptx::mbar_wait(mma_bar, (h - 1) & 1, status, 201);
-            if (tid == 0 && h + 1 < NH) {
-                ptx::mbar_expect_tx(&full[(h + 1) & 1], k2b::WO_STAGE);
-                ptx::tma_load_2d(sm + k2b::WO0 + ((h + 1) & 1) * k2b::WO_STAGE, &map_wo, 0, (set * NH + h + 1) * 64, &full[(h + 1) & 1]);
-            }
-        }
-        // ---- V' = E * box3(R) on the 8 x 16 tile: 16 columns x 8 chunks x 2 row segments -> A operand ------
-        if (tid < 256) {
-            const int q = tid & 7, c = (tid >> 3) & 15, r0 = (tid >> 7) * 4;
-            float hp2[8], hp1[8];
+    } else if (warp == 19) {
+        // ================= UMMA issuer ====================================================================
+        if (lane == 0) {
+            const uint32_t idesc = ptx::umma_idesc_bf16(128, 64);
+            for (int k = 0; k < my_tiles; ++k) {
+                const int ab = k & 1, w = k >> 1;
+                for (int h = 0; h < NH; ++h) {
+                    const int i = k * NH + h, s = i % 3, grp = h & 1, v = i >> 1;
+                    if (h == 0) ptx::mbar_wait(&acc_empty[ab], (w & 1) ^ 1, status, 220);
+                    ptx::mbar_wait(&full[grp * 3 + s], (i / 6) & 1, status, 221);
+                    ptx::mbar_wait(&vp_full[grp], v & 1, status, 222);
+                    ptx::tc_fence_after();
+                    const uint64_t da = ptx::umma_desc_sw128(ptx::smem_u32(sm + k2b::A_VP + grp * 16384));
+                    const uint64_t dw = ptx::umma_desc_sw128(ptx::smem_u32(sm + s * k2b::STAGE_BYTES + k2b::WO_OFF));
 #pragma unroll
-            for (int j = 0; j < 6; ++j) {
-                const uint8_t* row = vs + ((r0 + j) * 18 + c) * 128 + q * 16;
-                float a0[8], a1[8], a2[8], hs[8];
-                unpack8(*reinterpret_cast<const uint4*>(row), a0);
-                unpack8(*reinterpret_cast<const uint4*>(row + 128), a1);
-                unpack8(*reinterpret_cast<const uint4*>(row + 256), a2);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) hs[k] = (a0[k] + a1[k]) + a2[k];
-                if (j >= 2) {
-                    const int orow = r0 + j - 2;
-                    float e[8];
-                    unpack8(*reinterpret_cast<const uint4*>(es + ((orow + 2) * 20 + c + 2) * 128 + q * 16), e);
-#pragma unroll
-                    for (int k = 0; k < 8; ++k) e[k] *= (hp2[k] + hp1[k]) + hs[k];
-                    const uint4 out = pack8(e);
-                    *reinterpret_cast<uint4*>(a_vp + swz(orow * TBW + c, q)) = out;
-                    if (vprime != nullptr && ty0 + orow < g.H && tx0 + c < g.W)
-                        *reinterpret_cast<uint4*>(vprime + ((size_t)b * NH + h) * vplane +
-                                                  ((size_t)(ty0 + orow) * g.W + tx0 + c) * HD + q * 8) = out;
+                    for (int kk = 0; kk < 4; ++kk)
+                        ptx::umma_bf16(tmem + ab * 64, da + 2 * kk, dw + 2 * kk, idesc, h > 0 || kk > 0);
+                    ptx::umma_commit(&empty[s]);
+                    ptx::umma_commit(&vp_empty[grp]);
+                    if (h == NH - 1) ptx::umma_commit(&acc_full[ab]);
                 }
-#pragma unroll
-                for (int k = 0; k < 8; ++k) { hp2[k] = hp1[k]; hp1[k] = hs[k]; }
             }
         }
-        ptx::fence_proxy_async();
-        __syncthreads();
-        if (tid == 0) {
-            ptx::mbar_wait(&full[h & 1], (h >> 1) & 1, status, 202);
+    } else {
+        // ================= compute groups: group 0 = warps 0..8 takes even heads, group 1 = warps 9..17 odd ====
+        const int grp = warp >= 9 ? 1 : 0;
+        const int gt = tid - grp * k2b::GROUP;          // 0..287 inside the group
+        const int bar_main = 1 + grp, bar_ep = 3 + grp;
+        uint8_t* a_vp = sm + k2b::A_VP + grp * 16384;
+        float* red = reinterpret_cast<float*>(sm + k2b::RED) + grp * 256;
+        const size_t vplane = (size_t)g.H * g.W * HD;
+        K2Tile prev;
+        prev.index = -1;
+        for (int k = 0; k < my_tiles; ++k) {
+            const K2Tile t = k2_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x);
+            for (int h = grp; h < NH; h += 2) {
+                const int i = k * NH + h, s = i % 3, v = i >> 1;
+                uint8_t* es = sm + s * k2b::STAGE_BYTES + k2b::E_OFF;   // [12][20] cells x 128 B
+                uint8_t* vs = sm + s * k2b::STAGE_BYTES + k2b::V_OFF;   // [10][18] cells x 128 B: V, then R in place
+                ptx::mbar_wait(&full[grp * 3 + s], (i / 6) & 1, status, 230);
+
+                // ---- R = V / box3(E) on the 10 x 18 ring-extended tile: 18 columns x 8 chunks x 2 row segments ----
+                {
+                    const int q = gt & 7, c = (gt >> 3) % 18, r0 = (gt / 144) * 5;
+                    ptx::f2 hp2[4], hp1[4];
+#pragma unroll
+                    for (int j = 0; j < 7; ++j) {
+                        const uint8_t* row = es + ((r0 + j) * 20 + c) * 128 + q * 16;
+                        ptx::f2 e0[4], e1[4], e2[4], hs[4];
+                        unpack8p(*reinterpret_cast<const uint4*>(row), e0);
+                        unpack8p(*reinterpret_cast<const uint4*>(row + 128), e1);
+                        unpack8p(*reinterpret_cast<const uint4*>(row + 256), e2);
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) hs[n] = ptx::add2(ptx::add2(e0[n], e1[n]), e2[n]);
+                        if (j >= 2) {
+                            uint4* pv = reinterpret_cast<uint4*>(vs + ((r0 + j - 2) * 18 + c) * 128 + q * 16);
+                            ptx::f2 vv[4];
+                            unpack8p(*pv, vv);
+#pragma unroll
+                            for (int n = 0; n < 4; ++n) {
+                                float z0, z1;
+                                ptx::split_f2(ptx::add2(ptx::add2(hp2[n], hp1[n]), hs[n]), z0, z1);
+                                vv[n] = ptx::mul2(vv[n], ptx::make_f2(ptx::rcp(z0), ptx::rcp(z1)));
+                            }
+                            *pv = pack8p(vv);
+                        }
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) { hp2[n] = hp1[n]; hp1[n] = hs[n]; }
+                    }
+                }
+                ptx::bar_sync(bar_main, k2b::GROUP);
+                ptx::mbar_wait(&vp_empty[grp], (v & 1) ^ 1, status, 231);   // the UMMA two heads back is done with a_vp
+
+                // ---- V' = E * box3(R) on the 8 x 16 tile: 16 columns x 8 chunks x 2 row segments -> A operand ----
+                if (gt < 256) {
+                    const int q = gt & 7, c = (gt >> 3) & 15, r0 = (gt >> 7) * 4;
+                    ptx::f2 hp2[4], hp1[4];
+#pragma unroll
+                    for (int j = 0; j < 6; ++j) {
+                        const uint8_t* row = vs + ((r0 + j) * 18 + c) * 128 + q * 16;
+                        ptx::f2 a0[4], a1[4], a2[4], hs[4];
+                        unpack8p(*reinterpret_cast<const uint4*>(row), a0);
+                        unpack8p(*reinterpret_cast<const uint4*>(row + 128), a1);
+                        unpack8p(*reinterpret_cast<const uint4*>(row + 256), a2);
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) hs[n] = ptx::add2(ptx::add2(a0[n], a1[n]), a2[n]);
+                        if (j >= 2) {
+                            const int orow = r0 + j - 2;
+                            ptx::f2 e[4];
+                            unpack8p(*reinterpret_cast<const uint4*>(es + ((orow + 2) * 20 + c + 2) * 128 + q * 16), e);
+#pragma unroll
+                            for (int n = 0; n < 4; ++n) e[n] = ptx::mul2(e[n], ptx::add2(ptx::add2(hp2[n], hp1[n]), hs[n]));
+                            const uint4 out = pack8p(e);
+                            *reinterpret_cast<uint4*>(a_vp + swz(orow * TBW + c, q)) = out;
+                            if (vprime != nullptr && t.ty0 + orow < g.H && t.tx0 + c < g.W)
+                                *reinterpret_cast<uint4*>(vprime + ((size_t)t.b * NH + h) * vplane +
+                                                          ((size_t)(t.ty0 + orow) * g.W + t.tx0 + c) * HD + q * 8) = out;
+                        }
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) { hp2[n] = hp1[n]; hp1[n] = hs[n]; }
+                    }
+                }
+                ptx::fence_proxy_async();
+                ptx::bar_sync(bar_main, k2b::GROUP);
+                if (gt == 0) ptx::mbar_arrive(&vp_full[grp]);
+
+                // ---- epilogue of the previous tile, one tile behind, by the group of that tile's parity --------
+                if (h == 2 + grp && prev.index >= 0 && ((k - 1) & 1) == grp && gt < 256) {
+                    const int pk = k - 1, ab = pk & 1, w = pk >> 1;
+                    ptx::mbar_wait(&acc_full[ab], w & 1, status, 232);
+                    ptx::tc_fence_after();
+                    k2_epilogue(prev, tmem + ab * 64, X, scale, partial, red, bar_ep, gt, warp, g);
+                    ptx::tc_fence_before();
+                    ptx::mbar_arrive(&acc_empty[ab]);
+                }
+            }
+            prev = t;
+        }
+        if (my_tiles > 0 && ((my_tiles - 1) & 1) == grp && gt < 256) {
+            const int pk = my_tiles - 1, ab = pk & 1, w = pk >> 1;
+            ptx::mbar_wait(&acc_full[ab], w & 1, status, 233);
             ptx::tc_fence_after();
-            const uint64_t da = ptx::umma_desc_sw128(ptx::smem_u32(a_vp));
-            const uint64_t dw = ptx::umma_desc_sw128(ptx::smem_u32(sm + k2b::WO0 + (h & 1) * k2b::WO_STAGE));
-#pragma unroll
-            for (int k = 0; k < 4; ++k) ptx::umma_bf16(tmem, da + 2 * k, dw + 2 * k, idesc, h > 0 || k > 0);
-            ptx::umma_commit(mma_bar);
-        }
-    }
-    ptx::mbar_wait(mma_bar, (NH - 1) & 1, status, 203);
-    ptx::tc_fence_after();
-
-    // ---- X+ = scale * X + dt * Y (bf16, in place) and the per-channel sums of what was stored -------------------
-    if (warp < 8) {
-        const int quad = warp & 3, half = warp >> 2;
-        const int m = quad * 32 + lane;
-        const int r = ty0 + (m >> 4), x = tx0 + (m & 15);
-        const bool valid = r < g.H && x < g.W;
-        __nv_bfloat16* px = X + (size_t)b * xplane + ((size_t)g.xrow(r) * g.W + (valid ? x : 0)) * NC;
-#pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-            const int c0 = half * 32 + sub * 16;
-            uint32_t ry[16];
-            ptx::tmem_ld16(tmem + ((uint32_t)(quad * 32) << 16) + c0, ry);
-            ptx::tmem_ld_wait();
-            float xo[16];
-            if (valid) {
-                float f0[8], f1[8];
-                unpack8(*reinterpret_cast<const uint4*>(px + c0), f0);
-                unpack8(*reinterpret_cast<const uint4*>(px + c0 + 8), f1);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    xo[k] = fmaf(g.dt, __uint_as_float(ry[k]), f0[k] * scale_s[c0 + k]);
-                    xo[8 + k] = fmaf(g.dt, __uint_as_float(ry[8 + k]), f1[k] * scale_s[c0 + 8 + k]);
-                }
-                uint32_t pk[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    pk[k] = pack_bf16(xo[2 * k], xo[2 * k + 1]);
-                    xo[2 * k] = bf16_lo(pk[k]);          // sum what is stored, after rounding
-                    xo[2 * k + 1] = bf16_hi(pk[k]);
-                }
-                *reinterpret_cast<uint4*>(px + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                *reinterpret_cast<uint4*>(px + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-            } else {
-#pragma unroll
-                for (int k = 0; k < 16; ++k) xo[k] = 0.f;
-            }
-#pragma unroll
-            for (int k = 0; k < 16; k += 4)
-                *reinterpret_cast<float4*>(red + m * 64 + c0 + k) = make_float4(xo[k], xo[k + 1], xo[k + 2], xo[k + 3]);
+            k2_epilogue(prev, tmem + ab * 64, X, scale, partial, red, bar_ep, gt, warp, g);
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&acc_empty[ab]);
         }
     }
     ptx::tc_fence_before();
     __syncthreads();
-    if (tid < NC) {
-        float t = 0.f;
-        for (int m = 0; m < 128; ++m) t += red[m * 64 + tid];
-        partial[((size_t)b * gridDim.x + blockIdx.x) * NC + tid] = t;
-    }
     if (warp == 0) ptx::tmem_dealloc(tmem, k2b::TMEM_COLS);
 }
 
@@ -419,7 +547,7 @@ inline const char* bf16_error() { return bf16_error_ref(); }
 
 inline void bf16_plan(Bf16Plan& p, const Geom& g) {
     p.tiles_x = (g.W + TBW - 1) / TBW;
-    p.k1_tiles = p.tiles_x * ((g.ev_rows() + TBH - 1) / TBH);
+    p.k1_tiles = p.tiles_x * ((g.H + 2 * g.he + TBH - 1) / TBH);
     p.k2_tiles = p.tiles_x * ((g.H + TBH - 1) / TBH);
 }
 
@@ -438,8 +566,21 @@ inline int make_weight_map(EncodeTiledFn enc, CUtensorMap* map, const void* base
     return r == CUDA_SUCCESS ? 0 : -1;
 }
 
-// Tensor maps over the weight arrays and the kernels' shared-memory opt-in.  Returns 0 on success.
-inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16* wo, int sets) {
+// Tile map over the E or V planes: [planes][ev_h][ev_w][64] bf16, box 64 x box_w x box_h x 1, no swizzle.
+inline int make_plane_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, const Geom& g, uint32_t box_w, uint32_t box_h) {
+    const cuuint64_t dims[4] = {64, (cuuint64_t)g.ev_w, (cuuint64_t)g.ev_h, (cuuint64_t)g.B * NH};
+    const cuuint64_t strides[3] = {128, (cuuint64_t)g.ev_w * 128, (cuuint64_t)g.ev_h * g.ev_w * 128};
+    const cuuint32_t box[4] = {64, box_w, box_h, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -1;
+}
+
+// Tensor maps over the weight arrays and the E/V planes, and the kernels' shared-memory opt-in.  0 on success.
+inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16* wo, int sets, const __nv_bfloat16* E,
+                      const __nv_bfloat16* V, const Geom& g, int num_sms) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
@@ -453,11 +594,17 @@ inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16*
         bf16_error_ref() = "cuTensorMapEncodeTiled rejected the weight layout";
         return -1;
     }
+    if (make_plane_map(enc, &p.map_e, E, g, TBW + 4, TBH + 4) || make_plane_map(enc, &p.map_v, V, g, TBW + 2, TBH + 2)) {
+        bf16_error_ref() = "cuTensorMapEncodeTiled rejected the E/V plane layout";
+        return -1;
+    }
     if (cudaFuncSetAttribute(k1_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, k1b::SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(k2_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, k2b::SMEM) != cudaSuccess) {
         bf16_error_ref() = "could not opt in to the kernels' dynamic shared memory";
         return -1;
     }
+    const long long total = (long long)p.k2_tiles * g.B;
+    p.k2_grid = (int)(total < num_sms ? total : num_sms);
     return 0;
 }
 
@@ -467,9 +614,10 @@ inline int bf16_k1(Bf16Plan& p, const __nv_bfloat16* X, const float* scale, cons
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
-inline int bf16_k2(Bf16Plan& p, __nv_bfloat16* X, const float* scale, const __nv_bfloat16* E, const __nv_bfloat16* V,
+inline int bf16_k2(Bf16Plan& p, __nv_bfloat16* X, const float* scale, const __nv_bfloat16*, const __nv_bfloat16*,
                    float* partial, __nv_bfloat16* vprime, int* status, const Geom& g, cudaStream_t st) {
-    k2_bf16<<<dim3(p.k2_tiles, g.B), K2B_THREADS, k2b::SMEM, st>>>(p.map_wo, X, scale, E, V, partial, vprime, status, g);
+    k2_bf16<<<p.k2_grid, k2b::THREADS, k2b::SMEM, st>>>(p.map_wo, p.map_e, p.map_v, X, scale, partial, vprime, status,
+                                                        p.k2_tiles * g.B, p.k2_tiles, g);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -21,10 +21,13 @@ struct Geom {
     int wrap_y;      // 1 = torus in y
     int per_set;     // grids per weight set
     int tiles_x;     // tiles per row of tiles
+    int ev_h, ev_w;  // rows and columns of one E/V plane.  fp32 path: H + 2*he rows of W cells.  bf16 path: the
+                     // plane carries a 2-cell apron all around, (H + 4) x (W + 4), holding wrapped copies (or, in
+                     // stripe mode, the computed halo rows), so the second kernel reads it without any wrap logic
     float dt;
 
     __host__ __device__ int state_rows() const { return H + 2 * hx; }
-    __host__ __device__ int ev_rows() const { return H + 2 * he; }
+    __host__ __device__ int ev_rows() const { return ev_h; }
     __device__ int wrap_x(int x) const { x %= W; return x < 0 ? x + W : x; }
     // physical row in the state buffer of own-coordinate row r
     __device__ int xrow(int r) const {

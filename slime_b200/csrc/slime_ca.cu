@@ -23,7 +23,7 @@ struct slime_ca {
     Geom g{};
     size_t esz = 4;                 // bytes per stored element
     void* X = nullptr;              // [B][H+2hx][W][64]
-    void* E = nullptr;              // [B][8][H+2he][W][64]
+    void* E = nullptr;              // [B][8][ev_h][ev_w][64] (see Geom)
     void* V = nullptr;
     void* vprime[2] = {nullptr, nullptr};
     int vp_last = 0;                // index of the buffer holding the most recent V'
@@ -198,10 +198,12 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
     g.per_set = cfg->batch / cfg->n_weight_sets;
     g.dt = cfg->dt;
     h->esz = cfg->dtype == SLIME_CA_BF16 ? 2 : 4;
+    if (cfg->dtype == SLIME_CA_BF16) { g.ev_h = g.H + 2 * APRON; g.ev_w = g.W + 2 * APRON; }
+    else { g.ev_h = g.H + 2 * g.he; g.ev_w = g.W; }
     h->weights_set.assign(cfg->n_weight_sets, 0);
 
     const size_t xn = (size_t)g.B * g.state_rows() * g.W * NC;
-    const size_t en = (size_t)g.B * NH * g.ev_rows() * g.W * HD;
+    const size_t en = (size_t)g.B * NH * g.ev_h * g.ev_w * HD;
     int rc;
     if (is_bf16(h)) {
         bf16_plan(h->bf, g);
@@ -209,7 +211,7 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
         h->k1_tiles = h->bf.k1_tiles; h->k2_tiles = h->bf.k2_tiles;
     } else {
         g.tiles_x = (g.W + T32 - 1) / T32;
-        h->k1_tiles = g.tiles_x * ((g.ev_rows() + T32 - 1) / T32);
+        h->k1_tiles = g.tiles_x * ((g.H + 2 * g.he + T32 - 1) / T32);
         h->k2_tiles = g.tiles_x * ((g.H + T32 - 1) / T32);
         CK(h, cudaFuncSetAttribute(k1_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, K1F32_SMEM));
         CK(h, cudaFuncSetAttribute(k2_f32, cudaFuncAttributeMaxDynamicSharedMemorySize, K2F32_SMEM));
@@ -250,7 +252,8 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
     if (is_bf16(h)) {
         if ((rc = dev_alloc(h, &h->w1_bf16, sets * NH * 192 * 64))) return rc;
         if ((rc = dev_alloc(h, &h->wo_bf16, sets * NH * 64 * 64))) return rc;
-        if (bf16_setup(h->bf, h->w1_bf16, h->wo_bf16, (int)sets) != 0)
+        if (bf16_setup(h->bf, h->w1_bf16, h->wo_bf16, (int)sets, (const __nv_bfloat16*)h->E, (const __nv_bfloat16*)h->V, g,
+                       prop.multiProcessorCount) != 0)
             return fail(h, SLIME_CA_ECUDA, "tensor-map / kernel attribute set-up failed: " + std::string(bf16_error()));
     } else {
         if ((rc = dev_alloc(h, &h->wpiv_f32, sets * NH * NC * 192))) return rc;
