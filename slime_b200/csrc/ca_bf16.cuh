@@ -29,25 +29,31 @@ namespace slime {
 
 constexpr int TBH = 8, TBW = 16;      // tile: 8 rows x 16 columns = 128 cells
 constexpr int APRON = 2;              // apron of the E/V planes, cells
-constexpr int K1B_THREADS = 256;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct Bf16Plan {
-    int tiles_x = 1, k1_tiles = 1, k2_tiles = 1, k2_grid = 1;
+    int tiles_x = 1, k1_tiles = 1, k2_tiles = 1, k1_grid = 1, k2_grid = 1;
     CUtensorMap map_w1;   // [sets*8*192][64] bf16, box 64 x 192, 128B swizzle
     CUtensorMap map_wo;   // [sets*8*64][64]  bf16, box 64 x 64,  128B swizzle
     CUtensorMap map_e;    // E planes [B*8][H+4][W+4][64], box 64 x 20 x 12 x 1
     CUtensorMap map_v;    // V planes, box 64 x 18 x 10 x 1
+    CUtensorMap map_e_st; // E planes, store box 64 x 16 x 8 x 1, 128B swizzle
+    CUtensorMap map_v_st; // V planes, store box
 };
 
 // ---- shared-memory maps (byte offsets from a 1024-aligned base) -------------------------------------------
 namespace k1b {
-constexpr int A_X = 0, A_CONV = 16384, W0 = 32768, W_STAGE = 24576, XH = W0 + 2 * W_STAGE;   // 81920
-constexpr int XH_BYTES = 10 * 18 * 128;                                                          // 23040
-constexpr int SCALE = XH + XH_BYTES, PRM_S = SCALE + 256, BARS = PRM_S + NH * PRM * 4, TMEM_PTR = BARS + 32;
+constexpr int A_X = 0;                                   // 2 x 16 KB: X operand of the current / next tile
+constexpr int A_CONV = 2 * 16384;                        // 4 x 16 KB: stencil operand slots, two per half
+constexpr int W0 = A_CONV + 4 * 16384, W_STAGE = 24576;  // 3 x 24 KB: Wp|Wi|Wv rows of a head
+constexpr int STG_E = W0 + 3 * W_STAGE, STG_V = STG_E + 16384;   // staging tiles of the TMA stores
+constexpr int XH = STG_V + 16384, XH_BYTES = 10 * 18 * 128;      // state halo tile, plain [10][18] cells x 128 B
+constexpr int BARS = XH + XH_BYTES, TMEM_PTR = BARS + 24 * 8;
 constexpr int BYTES = TMEM_PTR + 16;
 constexpr int SMEM = BYTES + 1024;    // slack for manual 1024-byte alignment
-constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t TMEM_COLS = 512;   // two accumulator buffers of 192 columns
+constexpr int THREADS = 576;
+static_assert(SMEM <= 227 * 1024, "k1 shared memory");
 }  // namespace k1b
 namespace k2b {
 constexpr int STAGES = 3;
@@ -86,214 +92,296 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
 __device__ __forceinline__ uint32_t swz(int m, int q) { return (uint32_t)(m * 128 + ((q ^ (m & 7)) << 4)); }
 
 // =============================================================================================================
-__global__ void __launch_bounds__(K1B_THREADS, 2)
-k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __nv_bfloat16* __restrict__ X,
-        const float* __restrict__ scale, const float* __restrict__ prm, __nv_bfloat16* __restrict__ E,
-        __nv_bfloat16* __restrict__ V, int* __restrict__ status, Geom g) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t* sm = align1024(smem_raw);
-    uint8_t* a_x = sm + k1b::A_X;
-    uint8_t* a_conv = sm + k1b::A_CONV;
-    uint8_t* xh = sm + k1b::XH;
-    float* scale_s = reinterpret_cast<float*>(sm + k1b::SCALE);
-    float* prm_s = reinterpret_cast<float*>(sm + k1b::PRM_S);
-    uint64_t* full = reinterpret_cast<uint64_t*>(sm + k1b::BARS);      // [2] weight stages
-    uint64_t* mma_bar = full + 2;
-    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(sm + k1b::TMEM_PTR);
-
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int b = blockIdx.y;
-    const int tx0 = (blockIdx.x % g.tiles_x) * TBW;
-    const int ty0 = (blockIdx.x / g.tiles_x) * TBH - g.he;
-    const int set = b / g.per_set;
-    const size_t xplane = (size_t)g.state_rows() * g.W * NC;
-    const size_t eplane = (size_t)g.ev_h * g.ev_w * HD;
-
-    if (tid == 0) {
-        ptx::mbar_init(&full[0], 1);
-        ptx::mbar_init(&full[1], 1);
-        ptx::mbar_init(mma_bar, 1);
-        ptx::fence_barrier_init();
-        ptx::prefetch_tmap(&map_w1);
-    }
-    if (warp == 0) ptx::tmem_alloc(tmem_ptr, k1b::TMEM_COLS);
-    if (tid < NC) scale_s[tid] = scale[b * NC + tid];
-    if (tid < NH * PRM) prm_s[tid] = prm[(size_t)set * NH * PRM + tid];
-    ptx::tc_fence_before();
-    __syncthreads();
-    ptx::tc_fence_after();
-    const uint32_t tmem = *tmem_ptr;
-
-    if (tid == 0) {
-        for (int s = 0; s < 2; ++s) {
-            ptx::mbar_expect_tx(&full[s], k1b::W_STAGE);
-            ptx::tma_load_2d(sm + k1b::W0 + s * k1b::W_STAGE, &map_w1, 0, (set * NH + s) * 192, &full[s]);
-        }
-    }
-
-    // state halo tile (10 x 18 cells), pending renormalisation scale applied, kept as bf16
-    for (int i = tid; i < 180 * 8; i += K1B_THREADS) {
-        const int q = i & 7, cell = i >> 3;
-        const int hy = cell / 18, hx = cell % 18;
-        const int r = ty0 + hy - 1, x = g.wrap_x(tx0 + hx - 1);
-        const uint4 raw = *reinterpret_cast<const uint4*>(X + (size_t)b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC + q * 8);
-        float f[8];
-        unpack8(raw, f);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) f[k] *= scale_s[q * 8 + k];
-        const uint4 v = pack8(f);
-        *reinterpret_cast<uint4*>(xh + cell * 128 + q * 16) = v;
-        if (hy >= 1 && hy <= TBH && hx >= 1 && hx <= TBW)
-            *reinterpret_cast<uint4*>(a_x + swz((hy - 1) * TBW + hx - 1, q)) = v;
-    }
-    ptx::fence_proxy_async();
-    __syncthreads();
-
-    const uint32_t idesc_u = ptx::umma_idesc_bf16(128, 64);
-    const uint32_t idesc_iv = ptx::umma_idesc_bf16(128, 128);
-    const int quad = warp & 3, half = warp >> 2;
-    const int m_ep = quad * 32 + lane;                     // TMEM lane = cell of the tile this thread finishes
-    const int r_ep = ty0 + (m_ep >> 4), x_ep = tx0 + (m_ep & 15);
-    const bool valid_ep = r_ep < g.H + g.he && x_ep < g.W;
-    const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16);
-
-    // Where this thread's cell goes inside a plane: its own position and the apron positions that wrap onto it.
-    // Grids narrower or shorter than twice the apron can wrap more than once; they take the general loop below.
-    const bool tiny = g.W < 2 * APRON || (g.wrap_y && g.H < 2 * APRON);
-    const size_t own_off = ((size_t)(r_ep + APRON) * g.ev_w + x_ep + APRON) * HD;
-    size_t dup_off[3];
-    int ndup = 0;
-    if (valid_ep && !tiny) {
-        const int xd = x_ep < APRON ? x_ep + g.W : (x_ep >= g.W - APRON ? x_ep - g.W : -100);
-        const int rd = !g.wrap_y ? -100 : (r_ep < APRON ? r_ep + g.H : (r_ep >= g.H - APRON ? r_ep - g.H : -100));
-        if (xd != -100) dup_off[ndup++] = ((size_t)(r_ep + APRON) * g.ev_w + xd + APRON) * HD;
-        if (rd != -100) dup_off[ndup++] = ((size_t)(rd + APRON) * g.ev_w + x_ep + APRON) * HD;
-        if (xd != -100 && rd != -100) dup_off[ndup++] = ((size_t)(rd + APRON) * g.ev_w + xd + APRON) * HD;
-    }
-
-    for (int h = 0; h < NH; ++h) {
-        // ---- 3x3 stencil of head h on the state tile -> A operand ------------------------------------------
-        float kt[9];
-#pragma unroll
-        for (int t = 0; t < 9; ++t) kt[t] = prm_s[h * PRM + t];
-#pragma unroll 1
-        for (int pass = 0; pass < 4; ++pass) {
-            const int m = pass * 32 + (tid >> 3), q = tid & 7;
-            const int cy = m >> 4, cx = m & 15;
-            float acc[8];
-#pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = 0.f;
-#pragma unroll
-            for (int t = 0; t < 9; ++t) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(xh + ((cy + t / 3) * 18 + cx + t % 3) * 128 + q * 16);
-                float f[8];
-                unpack8(raw, f);
-#pragma unroll
-                for (int k = 0; k < 8; ++k) acc[k] = fmaf(kt[t], f[k], acc[k]);
-            }
-            *reinterpret_cast<uint4*>(a_conv + swz(m, q)) = pack8(acc);
-        }
-        ptx::fence_proxy_async();
-        __syncthreads();
-
-        // ---- projections: U | I | V into TMEM columns [0,64) | [64,128) | [128,192) -------------------------
-        if (tid == 0) {
-            ptx::mbar_wait(&full[h & 1], (h >> 1) & 1, status, 101);
-            ptx::tc_fence_after();
-            const uint32_t wb = ptx::smem_u32(sm + k1b::W0 + (h & 1) * k1b::W_STAGE);
-            const uint64_t da = ptx::umma_desc_sw128(ptx::smem_u32(a_conv));
-            const uint64_t dx = ptx::umma_desc_sw128(ptx::smem_u32(a_x));
-            const uint64_t dwp = ptx::umma_desc_sw128(wb);
-            const uint64_t dwiv = ptx::umma_desc_sw128(wb + 64 * 128);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) ptx::umma_bf16(tmem, da + 2 * k, dwp + 2 * k, idesc_u, k > 0);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) ptx::umma_bf16(tmem + 64, dx + 2 * k, dwiv + 2 * k, idesc_iv, k > 0);
-            ptx::umma_commit(mma_bar);
-        }
-        ptx::mbar_wait(mma_bar, h & 1, status, 102);
-        ptx::tc_fence_after();
-        if (tid == 0 && h + 2 < NH) {       // the stage just consumed is free: fetch the weights of head h+2
-            ptx::mbar_expect_tx(&full[h & 1], k1b::W_STAGE);
-            ptx::tma_load_2d(sm + k1b::W0 + (h & 1) * k1b::W_STAGE, &map_w1, 0, (set * NH + h + 2) * 192, &full[h & 1]);
-        }
-
-        // ---- epilogue: growth bell, activation, E = exp(A); E and V to global ---------------------------------
-        const float mu = prm_s[h * PRM + 9], nisl2 = prm_s[h * PRM + 10] * LOG2E;
-        __nv_bfloat16* Eh = E + ((size_t)b * NH + h) * eplane;
-        __nv_bfloat16* Vh = V + ((size_t)b * NH + h) * eplane;
-#pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-            const int c0 = half * 32 + sub * 16;
-            uint32_t ru[16], ri[16], rv[16];
-            ptx::tmem_ld16(t_lane + c0, ru);
-            ptx::tmem_ld16(t_lane + 64 + c0, ri);
-            ptx::tmem_ld16(t_lane + 128 + c0, rv);
-            ptx::tmem_ld_wait();
-            uint32_t pe[8], pv[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                float e2[2];
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const float z = __uint_as_float(ru[2 * j + k]) - mu;
-                    const float gr = fmaf(2.f, ptx::ex2(z * z * nisl2), -1.f);
-                    const float a = fminf(fmaxf(gr * __uint_as_float(ri[2 * j + k]), -80.f), 80.f);
-                    e2[k] = ptx::ex2(a * LOG2E);
-                }
-                pe[j] = pack_bf16(e2[0], e2[1]);
-                pv[j] = pack_bf16(__uint_as_float(rv[2 * j]), __uint_as_float(rv[2 * j + 1]));
-            }
-            const uint4 e_lo = make_uint4(pe[0], pe[1], pe[2], pe[3]), e_hi = make_uint4(pe[4], pe[5], pe[6], pe[7]);
-            const uint4 v_lo = make_uint4(pv[0], pv[1], pv[2], pv[3]), v_hi = make_uint4(pv[4], pv[5], pv[6], pv[7]);
-            if (valid_ep) {
-                if (!tiny) {
-#pragma unroll
-                    for (int d = 0; d < 4; ++d) {
-                        if (d > ndup) break;
-                        const size_t off = (d == 0 ? own_off : dup_off[d - 1]) + c0;
-                        uint4* pE = reinterpret_cast<uint4*>(Eh + off);
-                        uint4* pV = reinterpret_cast<uint4*>(Vh + off);
-                        pE[0] = e_lo; pE[1] = e_hi; pV[0] = v_lo; pV[1] = v_hi;
-                    }
-                } else {
-                    for (int ky = -2 * APRON; ky <= 2 * APRON; ++ky)
-                        for (int kx = -2 * APRON; kx <= 2 * APRON; ++kx) {
-                            if (ky != 0 && !g.wrap_y) continue;
-                            const int rr = r_ep + ky * g.H, xx = x_ep + kx * g.W;
-                            if (rr < -APRON || rr >= g.H + APRON || xx < -APRON || xx >= g.W + APRON) continue;
-                            const size_t off = ((size_t)(rr + APRON) * g.ev_w + xx + APRON) * HD + c0;
-                            uint4* pE = reinterpret_cast<uint4*>(Eh + off);
-                            uint4* pV = reinterpret_cast<uint4*>(Vh + off);
-                            pE[0] = e_lo; pE[1] = e_hi; pV[0] = v_lo; pV[1] = v_hi;
-                        }
-                }
-            }
-        }
-        ptx::tc_fence_before();
-        __syncthreads();       // TMEM and a_conv are free for the next head
-    }
-    if (warp == 0) ptx::tmem_dealloc(tmem, k1b::TMEM_COLS);
-}
-
-// =============================================================================================================
-// k2: the tile a CTA-local tile index refers to
-struct K2Tile {
+// A tile of 8 x 16 cells: grid b, origin (ty0, tx0) in own coordinates, linear index over all grids.
+struct CaTile {
     int b, ty0, tx0, index;
 };
-__device__ __forceinline__ K2Tile k2_tile(int t, int tiles_per_grid, int tiles_x) {
-    K2Tile r;
+__device__ __forceinline__ CaTile ca_tile(int t, int tiles_per_grid, int tiles_x, int row0) {
+    CaTile r;
     r.index = t;
     r.b = t / tiles_per_grid;
     const int tt = t - r.b * tiles_per_grid;
-    r.ty0 = (tt / tiles_x) * TBH;
+    r.ty0 = (tt / tiles_x) * TBH + row0;
     r.tx0 = (tt % tiles_x) * TBW;
     return r;
 }
 
+// k1: persistent, warp-specialised, one CTA per SM (576 threads):
+//   warps 0-7   stencil group: loads the tile's state halo (scale applied) and the X operand, then its two
+//               4-warp halves take alternate heads: 3x3 stencil marching down columns in packed fp32 -> A operand
+//   warps 8-15  epilogue group: TMEM -> growth bell, E = exp(G*I) -> swizzled staging tiles -> TMA store of the
+//               whole tile (+ register stores of the apron duplicates of edge cells)
+//   warp 16     TMA producer of the per-head weight tiles (3-stage ring)
+//   warp 17     UMMA issuer: U (N=64) and I|V (N=128) into a double-buffered 192-column TMEM accumulator
+__global__ void __launch_bounds__(k1b::THREADS, 1)
+k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUtensorMap map_e_st,
+        const __grid_constant__ CUtensorMap map_v_st, const __nv_bfloat16* __restrict__ X,
+        const float* __restrict__ scale, const float* __restrict__ prm, __nv_bfloat16* __restrict__ E,
+        __nv_bfloat16* __restrict__ V, int* __restrict__ status, int n_tiles, int tiles_per_grid, Geom g) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* sm = align1024(smem_raw);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + k1b::BARS);
+    // one waiting party per barrier, observing every phase in turn
+    uint64_t* w_full = bars;            // [3] weight tile of an item landed             (waits: UMMA issuer)
+    uint64_t* w_empty = bars + 3;       // [3] ... and was consumed                      (waits: TMA producer)
+    uint64_t* ac_full = bars + 6;       // [4] stencil operand slot written              (waits: UMMA issuer)
+    uint64_t* ac_empty = bars + 10;     // [4] ... and consumed                          (waits: the half that owns the slot)
+    uint64_t* ax_full = bars + 14;      // [2] X operand of a tile written               (waits: UMMA issuer)
+    uint64_t* ax_empty = bars + 16;     // [2] ... all 8 heads of that tile issued+done  (waits: stencil group)
+    uint64_t* tm_full = bars + 18;      // [2] accumulator buffer holds an item          (waits: epilogue group)
+    uint64_t* tm_empty = bars + 20;     // [2] ... and was drained (256 arrivals)        (waits: UMMA issuer)
+    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(sm + k1b::TMEM_PTR);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int i = 0; i < 20; ++i) ptx::mbar_init(&bars[i], 1);
+        ptx::mbar_init(&tm_empty[0], 256);
+        ptx::mbar_init(&tm_empty[1], 256);
+        ptx::fence_barrier_init();
+        ptx::prefetch_tmap(&map_w1); ptx::prefetch_tmap(&map_e_st); ptx::prefetch_tmap(&map_v_st);
+    }
+    if (warp == 0) ptx::tmem_alloc(tmem_ptr, k1b::TMEM_COLS);
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem = *tmem_ptr;
+    const int my_tiles = n_tiles > (int)blockIdx.x ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const size_t xplane = (size_t)g.state_rows() * g.W * NC;
+    const size_t eplane = (size_t)g.ev_h * g.ev_w * HD;
+
+    if (warp == 16) {
+        // ================= TMA producer: weights of item i = (tile k, head h) into stage i % 3 ================
+        if (lane == 0) {
+            for (int k = 0; k < my_tiles; ++k) {
+                const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
+                const int set = t.b / g.per_set;
+                for (int h = 0; h < NH; ++h) {
+                    const int i = k * NH + h, ws = i % 3;
+                    ptx::mbar_wait(&w_empty[ws], ((i / 3) & 1) ^ 1, status, 110);
+                    ptx::mbar_expect_tx(&w_full[ws], k1b::W_STAGE);
+                    ptx::tma_load_2d(sm + k1b::W0 + ws * k1b::W_STAGE, &map_w1, 0, (set * NH + h) * 192, &w_full[ws]);
+                }
+            }
+        }
+    } else if (warp == 17) {
+        // ================= UMMA issuer =======================================================================
+        if (lane == 0) {
+            const uint32_t idesc_u = ptx::umma_idesc_bf16(128, 64);
+            const uint32_t idesc_iv = ptx::umma_idesc_bf16(128, 128);
+            for (int k = 0; k < my_tiles; ++k) {
+                const int xb = k & 1;
+                for (int h = 0; h < NH; ++h) {
+                    const int i = k * NH + h, ws = i % 3, half = h & 1, n = k * 4 + (h >> 1);
+                    const int slot = half * 2 + (n & 1), tb = i & 1;
+                    if (h == 0) ptx::mbar_wait(&ax_full[xb], (k >> 1) & 1, status, 120);
+                    ptx::mbar_wait(&w_full[ws], (i / 3) & 1, status, 121);
+                    ptx::mbar_wait(&ac_full[slot], (n >> 1) & 1, status, 122);
+                    ptx::mbar_wait(&tm_empty[tb], ((i >> 1) & 1) ^ 1, status, 123);
+                    ptx::tc_fence_after();
+                    const uint32_t wb = ptx::smem_u32(sm + k1b::W0 + ws * k1b::W_STAGE);
+                    const uint64_t da = ptx::umma_desc_sw128(ptx::smem_u32(sm + k1b::A_CONV + slot * 16384));
+                    const uint64_t dx = ptx::umma_desc_sw128(ptx::smem_u32(sm + k1b::A_X + xb * 16384));
+                    const uint64_t dwp = ptx::umma_desc_sw128(wb);
+                    const uint64_t dwiv = ptx::umma_desc_sw128(wb + 64 * 128);
+                    const uint32_t acc = tmem + tb * 192;
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) ptx::umma_bf16(acc, da + 2 * kk, dwp + 2 * kk, idesc_u, kk > 0);
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk) ptx::umma_bf16(acc + 64, dx + 2 * kk, dwiv + 2 * kk, idesc_iv, kk > 0);
+                    ptx::umma_commit(&w_empty[ws]);
+                    ptx::umma_commit(&ac_empty[slot]);
+                    ptx::umma_commit(&tm_full[tb]);
+                    if (h == NH - 1) ptx::umma_commit(&ax_empty[xb]);
+                }
+            }
+        }
+    } else if (warp < 8) {
+        // ================= stencil group ======================================================================
+        const int half = warp >> 2, st = tid & 127;
+        uint8_t* xh = sm + k1b::XH;
+        for (int k = 0; k < my_tiles; ++k) {
+            const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
+            const int set = t.b / g.per_set;
+            uint8_t* a_x = sm + k1b::A_X + (k & 1) * 16384;
+            ptx::bar_sync(1, 256);                                        // both halves are done with the last halo
+            ptx::mbar_wait(&ax_empty[k & 1], ((k >> 1) & 1) ^ 1, status, 130);
+            const float* sc = scale + t.b * NC;
+            for (int i = tid; i < 180 * 8; i += 256) {
+                const int q = i & 7, cell = i >> 3;
+                const int hy = cell / 18, hx = cell % 18;
+                const int r = t.ty0 + hy - 1, x = g.wrap_x(t.tx0 + hx - 1);
+                const uint4 raw = *reinterpret_cast<const uint4*>(X + (size_t)t.b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC + q * 8);
+                const float4 s0 = __ldg(reinterpret_cast<const float4*>(sc + q * 8));
+                const float4 s1 = __ldg(reinterpret_cast<const float4*>(sc + q * 8 + 4));
+                float f[8];
+                unpack8(raw, f);
+                f[0] *= s0.x; f[1] *= s0.y; f[2] *= s0.z; f[3] *= s0.w;
+                f[4] *= s1.x; f[5] *= s1.y; f[6] *= s1.z; f[7] *= s1.w;
+                const uint4 v = pack8(f);
+                *reinterpret_cast<uint4*>(xh + cell * 128 + q * 16) = v;
+                if (hy >= 1 && hy <= TBH && hx >= 1 && hx <= TBW)
+                    *reinterpret_cast<uint4*>(a_x + swz((hy - 1) * TBW + hx - 1, q)) = v;
+            }
+            ptx::fence_proxy_async();
+            ptx::bar_sync(1, 256);
+            if (tid == 0) ptx::mbar_arrive(&ax_full[k & 1]);
+
+            const int q = st & 7, x = st >> 3;
+            for (int h = half; h < NH; h += 2) {
+                const int n = k * 4 + (h >> 1), slot = half * 2 + (n & 1);
+                uint8_t* a_conv = sm + k1b::A_CONV + slot * 16384;
+                const float* kp = prm + ((size_t)set * NH + h) * PRM;
+                ptx::f2 kt[9];
+#pragma unroll
+                for (int tt = 0; tt < 9; ++tt) { const float kv = __ldg(kp + tt); kt[tt] = ptx::make_f2(kv, kv); }
+                ptx::mbar_wait(&ac_empty[slot], ((n >> 1) & 1) ^ 1, status, 131);
+                // input row j feeds output rows j (tap row 0), j-1 (tap row 1) and j-2 (tap row 2)
+                ptx::f2 s1[4], s2[4];
+#pragma unroll
+                for (int j = 0; j < 10; ++j) {
+                    const uint8_t* row = xh + (j * 18 + x) * 128 + q * 16;
+                    ptx::f2 c0[4], c1[4], c2[4], nw[4], md[4];
+                    unpack8p(*reinterpret_cast<const uint4*>(row), c0);
+                    unpack8p(*reinterpret_cast<const uint4*>(row + 128), c1);
+                    unpack8p(*reinterpret_cast<const uint4*>(row + 256), c2);
+                    if (j >= 2) {
+                        ptx::f2 o[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            o[e] = ptx::fma2(kt[6], c0[e], ptx::fma2(kt[7], c1[e], ptx::fma2(kt[8], c2[e], s2[e])));
+                        *reinterpret_cast<uint4*>(a_conv + swz((j - 2) * TBW + x, q)) = pack8p(o);
+                    }
+                    if (j >= 1 && j <= 8) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            md[e] = ptx::fma2(kt[3], c0[e], ptx::fma2(kt[4], c1[e], ptx::fma2(kt[5], c2[e], s1[e])));
+                    }
+                    if (j <= 7) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            nw[e] = ptx::fma2(kt[0], c0[e], ptx::fma2(kt[1], c1[e], ptx::mul2(kt[2], c2[e])));
+                    }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { s2[e] = md[e]; s1[e] = nw[e]; }
+                }
+                ptx::fence_proxy_async();
+                ptx::bar_sync(2 + half, 128);
+                if (st == 0) ptx::mbar_arrive(&ac_full[slot]);
+            }
+        }
+    } else {
+        // ================= epilogue group (warps 8..15) ========================================================
+        const int et = tid - 256, quad = warp & 3, half = (warp - 8) >> 2;
+        const int m_ep = quad * 32 + lane;                 // TMEM lane = cell of the tile this thread finishes
+        uint8_t* stg_e = sm + k1b::STG_E;
+        uint8_t* stg_v = sm + k1b::STG_V;
+        const bool tiny = g.W < 2 * APRON || (g.wrap_y && g.H < 2 * APRON);
+        for (int k = 0; k < my_tiles; ++k) {
+            const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
+            const int set = t.b / g.per_set;
+            const int r_ep = t.ty0 + (m_ep >> 4), x_ep = t.tx0 + (m_ep & 15);
+            const bool valid_ep = r_ep < g.H + g.he && x_ep < g.W;
+            // Apron positions that wrap onto this thread's cell (the TMA store below covers the cell itself and
+            // whatever hangs over the far edge).  Grids narrower or shorter than twice the apron can wrap more
+            // than once and take the general loop.
+            size_t dup_off[3];
+            int ndup = 0;
+            if (valid_ep && !tiny) {
+                const int xd = x_ep < APRON ? x_ep + g.W : (x_ep >= g.W - APRON ? x_ep - g.W : -100);
+                const int rd = !g.wrap_y ? -100 : (r_ep < APRON ? r_ep + g.H : (r_ep >= g.H - APRON ? r_ep - g.H : -100));
+                if (xd != -100) dup_off[ndup++] = ((size_t)(r_ep + APRON) * g.ev_w + xd + APRON) * HD;
+                if (rd != -100) dup_off[ndup++] = ((size_t)(rd + APRON) * g.ev_w + x_ep + APRON) * HD;
+                if (xd != -100 && rd != -100) dup_off[ndup++] = ((size_t)(rd + APRON) * g.ev_w + xd + APRON) * HD;
+            }
+            for (int h = 0; h < NH; ++h) {
+                const int i = k * NH + h, tb = i & 1;
+                const float* kp = prm + ((size_t)set * NH + h) * PRM;
+                const float mu = __ldg(kp + 9), nisl2 = __ldg(kp + 10) * LOG2E;
+                ptx::mbar_wait(&tm_full[tb], (i >> 1) & 1, status, 140);
+                ptx::tc_fence_after();
+                const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16) + tb * 192;
+                uint32_t pe[2][8], pv[2][8];
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+                    const int c0 = half * 32 + sub * 16;
+                    uint32_t ru[16], ri[16], rv[16];
+                    ptx::tmem_ld16(t_lane + c0, ru);
+                    ptx::tmem_ld16(t_lane + 64 + c0, ri);
+                    ptx::tmem_ld16(t_lane + 128 + c0, rv);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float e2[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const float z = __uint_as_float(ru[2 * j + e]) - mu;
+                            const float gr = fmaf(2.f, ptx::ex2(z * z * nisl2), -1.f);
+                            const float a = fminf(fmaxf(gr * __uint_as_float(ri[2 * j + e]), -80.f), 80.f);
+                            e2[e] = ptx::ex2(a * LOG2E);
+                        }
+                        pe[sub][j] = pack_bf16(e2[0], e2[1]);
+                        pv[sub][j] = pack_bf16(__uint_as_float(rv[2 * j]), __uint_as_float(rv[2 * j + 1]));
+                    }
+                }
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(&tm_empty[tb]);                  // the accumulator buffer is free again
+                if (et == 0) ptx::bulk_wait_read0();              // the last TMA stores are done reading the staging
+                ptx::bar_sync(4, 256);
+#pragma unroll
+                for (int sub = 0; sub < 2; ++sub) {
+                    const int qa = half * 4 + sub * 2;
+                    const uint4 e_lo = make_uint4(pe[sub][0], pe[sub][1], pe[sub][2], pe[sub][3]);
+                    const uint4 e_hi = make_uint4(pe[sub][4], pe[sub][5], pe[sub][6], pe[sub][7]);
+                    const uint4 v_lo = make_uint4(pv[sub][0], pv[sub][1], pv[sub][2], pv[sub][3]);
+                    const uint4 v_hi = make_uint4(pv[sub][4], pv[sub][5], pv[sub][6], pv[sub][7]);
+                    *reinterpret_cast<uint4*>(stg_e + swz(m_ep, qa)) = e_lo;
+                    *reinterpret_cast<uint4*>(stg_e + swz(m_ep, qa + 1)) = e_hi;
+                    *reinterpret_cast<uint4*>(stg_v + swz(m_ep, qa)) = v_lo;
+                    *reinterpret_cast<uint4*>(stg_v + swz(m_ep, qa + 1)) = v_hi;
+                    if (valid_ep && (ndup > 0 || tiny)) {
+                        __nv_bfloat16* Eh = E + ((size_t)t.b * NH + h) * eplane + half * 32 + sub * 16;
+                        __nv_bfloat16* Vh = V + ((size_t)t.b * NH + h) * eplane + half * 32 + sub * 16;
+                        if (!tiny) {
+                            for (int d = 0; d < ndup; ++d) {
+                                uint4* pE = reinterpret_cast<uint4*>(Eh + dup_off[d]);
+                                uint4* pV = reinterpret_cast<uint4*>(Vh + dup_off[d]);
+                                pE[0] = e_lo; pE[1] = e_hi; pV[0] = v_lo; pV[1] = v_hi;
+                            }
+                        } else {
+                            for (int ky = -2 * APRON; ky <= 2 * APRON; ++ky)
+                                for (int kx = -2 * APRON; kx <= 2 * APRON; ++kx) {
+                                    if ((ky != 0 && !g.wrap_y) || (ky == 0 && kx == 0)) continue;
+                                    const int rr = r_ep + ky * g.H, xx = x_ep + kx * g.W;
+                                    if (rr < -APRON || rr >= g.H + APRON || xx < -APRON || xx >= g.W + APRON) continue;
+                                    const size_t off = ((size_t)(rr + APRON) * g.ev_w + xx + APRON) * HD;
+                                    uint4* pE = reinterpret_cast<uint4*>(Eh + off);
+                                    uint4* pV = reinterpret_cast<uint4*>(Vh + off);
+                                    pE[0] = e_lo; pE[1] = e_hi; pV[0] = v_lo; pV[1] = v_hi;
+                                }
+                        }
+                    }
+                }
+                ptx::fence_proxy_async();
+                ptx::bar_sync(4, 256);
+                if (et == 0) {
+                    ptx::tma_store_4d(&map_e_st, stg_e, 0, t.tx0 + APRON, t.ty0 + APRON, t.b * NH + h);
+                    ptx::tma_store_4d(&map_v_st, stg_v, 0, t.tx0 + APRON, t.ty0 + APRON, t.b * NH + h);
+                    ptx::bulk_commit();
+                }
+            }
+        }
+        if (et == 0) ptx::bulk_wait0();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 0) ptx::tmem_dealloc(tmem, k1b::TMEM_COLS);
+}
+
+// =============================================================================================================
+
 // Epilogue of one finished tile, run by 8 warps (256 threads) of one compute group: X+ = scale*X + dt*Y in
 // place, and the tile's per-channel sums of the stored (rounded) values -> partial[tile][64].
-__device__ __forceinline__ void k2_epilogue(const K2Tile& t, uint32_t acc_taddr, __nv_bfloat16* __restrict__ X,
+__device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr, __nv_bfloat16* __restrict__ X,
                                             const float* __restrict__ scale, float* __restrict__ partial,
                                             float* red, int bar_id, int gt, int cta_warp, const Geom& g) {
     const int lane = gt & 31, quad = cta_warp & 3, half = (gt >> 5) >> 2;
@@ -394,7 +482,7 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
         // ================= TMA producer ===================================================================
         if (lane == 0) {
             for (int k = 0; k < my_tiles; ++k) {
-                const K2Tile t = k2_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x);
+                const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, 0);
                 const int set = t.b / g.per_set;
                 for (int h = 0; h < NH; ++h) {
                     const int i = k * NH + h, s = i % 3, u = i / 3;
@@ -439,10 +527,10 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
         uint8_t* a_vp = sm + k2b::A_VP + grp * 16384;
         float* red = reinterpret_cast<float*>(sm + k2b::RED) + grp * 256;
         const size_t vplane = (size_t)g.H * g.W * HD;
-        K2Tile prev;
+        CaTile prev;
         prev.index = -1;
         for (int k = 0; k < my_tiles; ++k) {
-            const K2Tile t = k2_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x);
+            const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, 0);
             for (int h = grp; h < NH; h += 2) {
                 const int i = k * NH + h, s = i % 3, v = i >> 1;
                 uint8_t* es = sm + s * k2b::STAGE_BYTES + k2b::E_OFF;   // [12][20] cells x 128 B
@@ -567,13 +655,14 @@ inline int make_weight_map(EncodeTiledFn enc, CUtensorMap* map, const void* base
 }
 
 // Tile map over the E or V planes: [planes][ev_h][ev_w][64] bf16, box 64 x box_w x box_h x 1, no swizzle.
-inline int make_plane_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, const Geom& g, uint32_t box_w, uint32_t box_h) {
+inline int make_plane_map(EncodeTiledFn enc, CUtensorMap* map, const void* base, const Geom& g, uint32_t box_w, uint32_t box_h,
+                          CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_NONE) {
     const cuuint64_t dims[4] = {64, (cuuint64_t)g.ev_w, (cuuint64_t)g.ev_h, (cuuint64_t)g.B * NH};
     const cuuint64_t strides[3] = {128, (cuuint64_t)g.ev_w * 128, (cuuint64_t)g.ev_h * g.ev_w * 128};
     const cuuint32_t box[4] = {64, box_w, box_h, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? 0 : -1;
 }
@@ -594,7 +683,9 @@ inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16*
         bf16_error_ref() = "cuTensorMapEncodeTiled rejected the weight layout";
         return -1;
     }
-    if (make_plane_map(enc, &p.map_e, E, g, TBW + 4, TBH + 4) || make_plane_map(enc, &p.map_v, V, g, TBW + 2, TBH + 2)) {
+    if (make_plane_map(enc, &p.map_e, E, g, TBW + 4, TBH + 4) || make_plane_map(enc, &p.map_v, V, g, TBW + 2, TBH + 2) ||
+        make_plane_map(enc, &p.map_e_st, E, g, TBW, TBH, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        make_plane_map(enc, &p.map_v_st, V, g, TBW, TBH, CU_TENSOR_MAP_SWIZZLE_128B)) {
         bf16_error_ref() = "cuTensorMapEncodeTiled rejected the E/V plane layout";
         return -1;
     }
@@ -603,14 +694,16 @@ inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16*
         bf16_error_ref() = "could not opt in to the kernels' dynamic shared memory";
         return -1;
     }
-    const long long total = (long long)p.k2_tiles * g.B;
+    const long long total = (long long)p.k2_tiles * g.B, total1 = (long long)p.k1_tiles * g.B;
     p.k2_grid = (int)(total < num_sms ? total : num_sms);
+    p.k1_grid = (int)(total1 < num_sms ? total1 : num_sms);
     return 0;
 }
 
 inline int bf16_k1(Bf16Plan& p, const __nv_bfloat16* X, const float* scale, const float* prm, __nv_bfloat16* E,
                    __nv_bfloat16* V, int* status, const Geom& g, cudaStream_t st) {
-    k1_bf16<<<dim3(p.k1_tiles, g.B), K1B_THREADS, k1b::SMEM, st>>>(p.map_w1, X, scale, prm, E, V, status, g);
+    k1_bf16<<<p.k1_grid, k1b::THREADS, k1b::SMEM, st>>>(p.map_w1, p.map_e_st, p.map_v_st, X, scale, prm, E, V, status,
+                                                        p.k1_tiles * g.B, p.k1_tiles, g);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
