@@ -167,6 +167,30 @@ long long slime_ca_launch_count(const slime_ca* h);
  */
 void launch_multi_head_ca(float* ca_state, float* weights, float* ca_output, int batch_size, int grid_size);
 
+/*
+ * Per-channel sums of a dense DEVICE state [batch][cells_per_grid][64] (fp32 or bf16) into DEVICE
+ * dev_sums[batch][64] (fp64), computed without allocating anything.  No counterpart in the reference.
+ *
+ * For callers that can not call cudaMalloc where they need a state's channel masses: a host loop that has
+ * given the whole device to its own memory pool (so a cudaMalloc fails), or a latency-critical loop that can
+ * not take the device-wide synchronisation cudaMalloc / cudaFree imply.  This call makes no cudaMalloc, no
+ * cudaFree and no allocating library call; its only scratch is a 2 MiB array built into the library image
+ * (every GPU that loads the library holds it until the process exits).
+ *
+ * Limit: batch * ceil(cells_per_grid / 256) <= 8192 (at most 2 097 152 cells per call); larger requests return
+ * SLIME_CA_EINVAL and slime_ca_static_error() says so.  The first call on each device resolves the address of
+ * the built-in array; make that first call outside any stream capture.  All calls on a device share the array,
+ * which keeps whatever the last call left: nothing needs to start at zero (every slot a call reads it has
+ * written first), but two calls whose kernels overlap on the GPU (different streams, different host threads)
+ * race on it - run them one after the other.  Work is enqueued on `stream` of the CURRENT device; no
+ * synchronisation.  Same numbers as slime_ca_set_state_device + slime_ca_get_mass up to fp64 summation order.
+ */
+int slime_ca_channel_sums_static(const void* dev_state, int dtype, int batch, int cells_per_grid, double* dev_sums,
+                                 void* stream);
+
+/* Text of the last failure of slime_ca_channel_sums_static on the calling thread ("" after a success). */
+const char* slime_ca_static_error(void);
+
 #ifdef __cplusplus
 }
 #endif

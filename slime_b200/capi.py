@@ -24,6 +24,7 @@ SYMBOLS = (
     "slime_ca_get_state_device", "slime_ca_set_mass", "slime_ca_get_mass", "slime_ca_step",
     "slime_ca_step_partial", "slime_ca_step_finish", "slime_ca_step_timed", "slime_ca_buffer", "slime_ca_fitness",
     "slime_ca_lift_images", "slime_ca_pool_readout", "slime_ca_launch_count", "launch_multi_head_ca",
+    "slime_ca_channel_sums_static", "slime_ca_static_error",
 )
 
 
@@ -75,6 +76,9 @@ def lib():
         L.slime_ca_launch_count.restype = ctypes.c_longlong
         L.launch_multi_head_ca.argtypes = [vp, vp, vp, ctypes.c_int, ctypes.c_int]
         L.launch_multi_head_ca.restype = None
+        L.slime_ca_channel_sums_static.argtypes = [vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, vp]
+        L.slime_ca_static_error.argtypes = []
+        L.slime_ca_static_error.restype = ctypes.c_char_p
         _lib = L
     return _lib
 

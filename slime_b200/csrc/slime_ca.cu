@@ -618,3 +618,75 @@ void launch_multi_head_ca(float* ca_state, float* weights, float* ca_output, int
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Per-channel sums without any allocation.
+//
+// Some callers of this library can not allocate device memory at the point where they need a state's channel
+// masses: a host loop that has handed the whole device to its own pool (a framework's caching allocator, or the
+// reference's habit of carving every buffer out of pools made once in create_organism, slime/runtime.cu:275-326),
+// where a cudaMalloc simply fails, and latency-critical generation loops, where the implicit device-wide
+// synchronisation of cudaMalloc / cudaFree is not acceptable.  For them the two-stage reduction below keeps its
+// scratch (the per-chunk partial sums) in a fixed array that is part of the loaded library image.
+//
+// The array is a file-scope __device__ object: every GPU that loads the library holds its 2 MiB until the process
+// exits.  In host code its name is only a handle for the runtime, not a device address, so the address is looked up
+// once per device with cudaGetSymbolAddress (below) and that pointer is what the kernels receive.
+constexpr int STATIC_MAX_CHUNKS = 8192;    // 256-cell chunks over all grids of one call: at most 2 097 152 cells
+static __device__ __align__(256) float g_static_partials[(size_t)STATIC_MAX_CHUNKS * NC];
+
+namespace {
+constexpr int STATIC_MAX_DEVICES = 64;
+float* g_static_partials_addr[STATIC_MAX_DEVICES] = {};
+thread_local std::string g_static_error;
+
+int static_fail(int code, const std::string& msg) {
+    g_static_error = msg;
+    return code;
+}
+}  // namespace
+
+extern "C" {
+
+const char* slime_ca_static_error(void) { return g_static_error.c_str(); }
+
+int slime_ca_channel_sums_static(const void* dev_state, int dtype, int batch, int cells_per_grid, double* dev_sums,
+                                 void* stream) {
+    if (!dev_state || !dev_sums) return static_fail(SLIME_CA_EINVAL, "null pointer");
+    if (dtype != SLIME_CA_F32 && dtype != SLIME_CA_BF16) return static_fail(SLIME_CA_EINVAL, "dtype must be SLIME_CA_F32 or SLIME_CA_BF16");
+    if (batch <= 0 || cells_per_grid <= 0) return static_fail(SLIME_CA_EINVAL, "batch and cells_per_grid must be positive");
+    const long long chunks = ((long long)cells_per_grid + 255) / 256;
+    if (chunks * batch > STATIC_MAX_CHUNKS)
+        return static_fail(SLIME_CA_EINVAL, "too large for the built-in scratch: batch * ceil(cells_per_grid / 256) = " +
+                                                std::to_string(chunks * batch) + " exceeds " + std::to_string(STATIC_MAX_CHUNKS) +
+                                                " (use a handle and slime_ca_get_mass instead)");
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_fail(SLIME_CA_ECUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
+    if (dev < 0 || dev >= STATIC_MAX_DEVICES) return static_fail(SLIME_CA_EINVAL, "device ordinal out of range");
+    if (!g_static_partials_addr[dev]) {
+        // set-up, once per device, with that device current: resolve the device address of the scratch array
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_static_partials);
+        if (e != cudaSuccess || !p) return static_fail(SLIME_CA_ECUDA, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
+        g_static_partials_addr[dev] = p;
+    }
+    float* partial = g_static_partials_addr[dev];
+    cudaStream_t st = (cudaStream_t)stream;
+    Geom g{};
+    g.B = batch; g.H = cells_per_grid; g.W = 1; g.hx = 0; g.he = 0; g.wrap_y = 1; g.per_set = 1;
+    const dim3 grid((unsigned)chunks, (unsigned)batch);
+    if (dtype == SLIME_CA_BF16) k_channel_partials<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)dev_state, partial, g);
+    else k_channel_partials<float><<<grid, 256, 0, st>>>((const float*)dev_state, partial, g);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return static_fail(SLIME_CA_ECUDA, std::string("kernel launch: ") + cudaGetErrorString(e));
+    // one segment per grid: the fp64 second stage writes [batch][64] straight into the caller's buffer
+    k_reduce_partials<<<dim3(1, (unsigned)batch), 256, 0, st>>>(partial, (int)chunks, dev_sums);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return static_fail(SLIME_CA_ECUDA, std::string("kernel launch: ") + cudaGetErrorString(e));
+    g_static_error.clear();
+    return SLIME_CA_OK;
+}
+
+}  // extern "C"
+
