@@ -77,6 +77,14 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.rows)}
 
 
+# DRAM bytes per cell-update of each bf16 kernel, from the ncu captures summarised under profiles/
+# (k*_bf16_pipelined_batch8_128x128.txt: dram__bytes_read.sum + dram__bytes_write.sum over 131 072 cells).  The
+# capture is a batch of 8 grids (268 MB of E/V per kernel, larger than L2); traffic grows in proportion to the
+# cells, so a full launch is this figure times its cells.  k1's figure sits below its algorithmic bytes because
+# part of what it wrote was still dirty in the 126 MB L2 when the captured launch ended.
+NCU_DRAM_BYTES_PER_CELL = {"k1": (17.312e6 + 227.391e6) / 131072, "k2": (298.444e6 + 13.103e6) / 131072}
+
+
 def cpu_baseline(ca_steps_sample=2, grids=1):
     """The oracle's fp32 multithreaded transcription on a bounded sample: `grids` grids x `ca_steps_sample` steps."""
     from oracle import ca_oracle
@@ -99,7 +107,7 @@ def run_reference(args, rank, world):
     per_step = []
     base = None
     for i in range(args.warmup + args.steps):
-        base = cpu_baseline(ca_steps_sample=2, grids=1)
+        base = cpu_baseline(ca_steps_sample=CA_STEPS, grids=2)      # 2 of the 64 grids, all 64 steps: about 3 s
         if i >= args.warmup:
             per_step.append(base["value"])
     v = float(np.mean(per_step))
@@ -107,7 +115,8 @@ def run_reference(args, rank, world):
     line = {"impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": BATCH * GRID * GRID * CA_STEPS / v * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"X[{BATCH},{GRID},{GRID},64] x {CA_STEPS} CA steps (bounded sample per step, rate extrapolated)",
+            "config": {"workload": f"batched training-shape forward X[{BATCH},{GRID},{GRID},64], 8 heads x 64, {CA_STEPS} CA steps "
+                                   "per bench step (each step times 2 of the 64 grids for all 64 CA steps; rate extrapolated)",
                        "inputs": "seeded synthetic"},
             "cpu_baseline": base,
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
@@ -196,8 +205,10 @@ def main():
     dom_ms = max(kt[0], kt[1]) / S
     peak, peak_kind = measured_peaks()
     achieved = cells * ALG_BYTES[dom][args.dtype] / (dom_ms * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": dom, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+    traffic = cells * NCU_DRAM_BYTES_PER_CELL[dom] if args.dtype == "bf16" else None
+    roofline = {"bound": "hbm", "kernel": dom + "_" + args.dtype, "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
+                "algorithmic_bytes_per_launch": cells * ALG_BYTES[dom][args.dtype],
                 "ms_per_launch": dom_ms, "k1_ms": kt[0] / S, "k2_ms": kt[1] / S, "other_ms": kt[2] / S}
 
     # ---- end to end through the C ABI: host state in, 64 steps, host state out -------------------
@@ -233,7 +244,7 @@ def main():
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
                 "state_finite_after_steps": finite_after}
         if not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_baseline(ca_steps_sample=4, grids=2)
+            line["cpu_baseline"] = cpu_baseline(ca_steps_sample=CA_STEPS, grids=8)   # 8 of the 64 grids: 10-15 s
         print(json.dumps(line), flush=True)
     h.close()
     if world > 1:
