@@ -48,7 +48,8 @@ constexpr int A_CONV = 2 * 16384;                        // 4 x 16 KB: stencil o
 constexpr int W0 = A_CONV + 4 * 16384, W_STAGE = 24576;  // 3 x 24 KB: Wp|Wi|Wv rows of a head
 constexpr int STG_E = W0 + 3 * W_STAGE, STG_V = STG_E + 16384;   // staging tiles of the TMA stores
 constexpr int XH = STG_V + 16384, XH_BYTES = 10 * 18 * 128;      // state halo tile, plain [10][18] cells x 128 B
-constexpr int BARS = XH + XH_BYTES, TMEM_PTR = BARS + 24 * 8;
+constexpr int PRM_ST = XH + XH_BYTES, PRM_EP = PRM_ST + NH * PRM * 4;   // per-tile copies of the head parameters
+constexpr int BARS = PRM_EP + NH * PRM * 4, TMEM_PTR = BARS + 24 * 8;
 constexpr int BYTES = TMEM_PTR + 16;
 constexpr int SMEM = BYTES + 1024;    // slack for manual 1024-byte alignment
 constexpr uint32_t TMEM_COLS = 512;   // two accumulator buffers of 192 columns
@@ -199,6 +200,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
         // ================= stencil group ======================================================================
         const int half = warp >> 2, st = tid & 127;
         uint8_t* xh = sm + k1b::XH;
+        float* prm_s = reinterpret_cast<float*>(sm + k1b::PRM_ST);
         for (int k = 0; k < my_tiles; ++k) {
             const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
             const int set = t.b / g.per_set;
@@ -206,6 +208,12 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
             ptx::bar_sync(1, 256);                                        // both halves are done with the last halo
             ptx::mbar_wait(&ax_empty[k & 1], ((k >> 1) & 1) ^ 1, status, 130);
             const float* sc = scale + t.b * NC;
+            if (tid < NH * PRM) prm_s[tid] = __ldg(prm + (size_t)set * NH * PRM + tid);
+            if (k + 1 < my_tiles && tid < 180) {       // next tile's halo cells: one 128-byte line each, into L2
+                const CaTile tn = ca_tile(blockIdx.x + (k + 1) * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
+                const int r = tn.ty0 + tid / 18 - 1, x = g.wrap_x(tn.tx0 + tid % 18 - 1);
+                ptx::prefetch_l2(X + (size_t)tn.b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC);
+            }
             for (int i = tid; i < 180 * 8; i += 256) {
                 const int q = i & 7, cell = i >> 3;
                 const int hy = cell / 18, hx = cell % 18;
@@ -230,10 +238,9 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
             for (int h = half; h < NH; h += 2) {
                 const int n = k * 4 + (h >> 1), slot = half * 2 + (n & 1);
                 uint8_t* a_conv = sm + k1b::A_CONV + slot * 16384;
-                const float* kp = prm + ((size_t)set * NH + h) * PRM;
                 ptx::f2 kt[9];
 #pragma unroll
-                for (int tt = 0; tt < 9; ++tt) { const float kv = __ldg(kp + tt); kt[tt] = ptx::make_f2(kv, kv); }
+                for (int tt = 0; tt < 9; ++tt) { const float kv = prm_s[h * PRM + tt]; kt[tt] = ptx::make_f2(kv, kv); }
                 ptx::mbar_wait(&ac_empty[slot], ((n >> 1) & 1) ^ 1, status, 131);
                 // input row j feeds output rows j (tap row 0), j-1 (tap row 1) and j-2 (tap row 2)
                 ptx::f2 s1[4], s2[4];
@@ -275,12 +282,16 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
         const int m_ep = quad * 32 + lane;                 // TMEM lane = cell of the tile this thread finishes
         uint8_t* stg_e = sm + k1b::STG_E;
         uint8_t* stg_v = sm + k1b::STG_V;
+        float* prm_e = reinterpret_cast<float*>(sm + k1b::PRM_EP);
         const bool tiny = g.W < 2 * APRON || (g.wrap_y && g.H < 2 * APRON);
         for (int k = 0; k < my_tiles; ++k) {
             const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
             const int set = t.b / g.per_set;
             const int r_ep = t.ty0 + (m_ep >> 4), x_ep = t.tx0 + (m_ep & 15);
             const bool valid_ep = r_ep < g.H + g.he && x_ep < g.W;
+            ptx::bar_sync(4, 256);                     // everyone is done with the last tile's parameters
+            if (et < NH * PRM) prm_e[et] = __ldg(prm + (size_t)set * NH * PRM + et);
+            ptx::bar_sync(4, 256);
             // Apron positions that wrap onto this thread's cell (the TMA store below covers the cell itself and
             // whatever hangs over the far edge).  Grids narrower or shorter than twice the apron can wrap more
             // than once and take the general loop.
@@ -295,8 +306,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
             }
             for (int h = 0; h < NH; ++h) {
                 const int i = k * NH + h, tb = i & 1;
-                const float* kp = prm + ((size_t)set * NH + h) * PRM;
-                const float mu = __ldg(kp + 9), nisl2 = __ldg(kp + 10) * LOG2E;
+                const float mu = prm_e[h * PRM + 9], nisl2 = prm_e[h * PRM + 10] * LOG2E;
                 ptx::mbar_wait(&tm_full[tb], (i >> 1) & 1, status, 140);
                 ptx::tc_fence_after();
                 const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16) + tb * 192;
@@ -399,13 +409,18 @@ __device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr,
         ptx::tmem_ld_wait();
         float xo[16];
         if (valid) {
-            float f0[8], f1[8];
+            float f0[8], f1[8], sv[16];
             unpack8(*reinterpret_cast<const uint4*>(px + c0), f0);
             unpack8(*reinterpret_cast<const uint4*>(px + c0 + 8), f1);
 #pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float4 s4 = __ldg(reinterpret_cast<const float4*>(sc + c0) + k);
+                sv[4 * k] = s4.x; sv[4 * k + 1] = s4.y; sv[4 * k + 2] = s4.z; sv[4 * k + 3] = s4.w;
+            }
+#pragma unroll
             for (int k = 0; k < 8; ++k) {
-                xo[k] = fmaf(g.dt, __uint_as_float(ry[k]), f0[k] * __ldg(sc + c0 + k));
-                xo[8 + k] = fmaf(g.dt, __uint_as_float(ry[8 + k]), f1[k] * __ldg(sc + c0 + 8 + k));
+                xo[k] = fmaf(g.dt, __uint_as_float(ry[k]), f0[k] * sv[k]);
+                xo[8 + k] = fmaf(g.dt, __uint_as_float(ry[8 + k]), f1[k] * sv[8 + k]);
             }
             uint32_t pk[8];
 #pragma unroll
@@ -493,6 +508,13 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
                     ptx::tma_load_2d(st + k2b::WO_OFF, &map_wo, 0, (set * NH + h) * 64, fb);
                     ptx::tma_load_4d(st + k2b::E_OFF, &map_e, 0, t.tx0, t.ty0, t.b * NH + h, fb);
                     ptx::tma_load_4d(st + k2b::V_OFF, &map_v, 0, t.tx0 + 1, t.ty0 + 1, t.b * NH + h, fb);
+                    // pull the item three ahead into L2 while this one streams into shared memory
+                    const int j = i + 3, kj = j / NH, hj = j % NH;
+                    if (kj < my_tiles) {
+                        const CaTile tj = ca_tile(blockIdx.x + kj * gridDim.x, tiles_per_grid, g.tiles_x, 0);
+                        ptx::tma_prefetch_4d(&map_e, 0, tj.tx0, tj.ty0, tj.b * NH + hj);
+                        ptx::tma_prefetch_4d(&map_v, 0, tj.tx0 + 1, tj.ty0 + 1, tj.b * NH + hj);
+                    }
                 }
             }
         }
@@ -544,12 +566,12 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
 #pragma unroll
                     for (int j = 0; j < 7; ++j) {
                         const uint8_t* row = es + ((r0 + j) * 20 + c) * 128 + q * 16;
-                        ptx::f2 e0[4], e1[4], e2[4], hs[4];
-                        unpack8p(*reinterpret_cast<const uint4*>(row), e0);
-                        unpack8p(*reinterpret_cast<const uint4*>(row + 128), e1);
-                        unpack8p(*reinterpret_cast<const uint4*>(row + 256), e2);
-#pragma unroll
-                        for (int n = 0; n < 4; ++n) hs[n] = ptx::add2(ptx::add2(e0[n], e1[n]), e2[n]);
+                        const uint4 e0 = *reinterpret_cast<const uint4*>(row);
+                        const uint4 e1 = *reinterpret_cast<const uint4*>(row + 128);
+                        const uint4 e2 = *reinterpret_cast<const uint4*>(row + 256);
+                        ptx::f2 hs[4];
+                        hs[0] = ptx::sum3_bf16x2(e0.x, e1.x, e2.x); hs[1] = ptx::sum3_bf16x2(e0.y, e1.y, e2.y);
+                        hs[2] = ptx::sum3_bf16x2(e0.z, e1.z, e2.z); hs[3] = ptx::sum3_bf16x2(e0.w, e1.w, e2.w);
                         if (j >= 2) {
                             uint4* pv = reinterpret_cast<uint4*>(vs + ((r0 + j - 2) * 18 + c) * 128 + q * 16);
                             ptx::f2 vv[4];
@@ -576,12 +598,12 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
 #pragma unroll
                     for (int j = 0; j < 6; ++j) {
                         const uint8_t* row = vs + ((r0 + j) * 18 + c) * 128 + q * 16;
-                        ptx::f2 a0[4], a1[4], a2[4], hs[4];
-                        unpack8p(*reinterpret_cast<const uint4*>(row), a0);
-                        unpack8p(*reinterpret_cast<const uint4*>(row + 128), a1);
-                        unpack8p(*reinterpret_cast<const uint4*>(row + 256), a2);
-#pragma unroll
-                        for (int n = 0; n < 4; ++n) hs[n] = ptx::add2(ptx::add2(a0[n], a1[n]), a2[n]);
+                        const uint4 a0 = *reinterpret_cast<const uint4*>(row);
+                        const uint4 a1 = *reinterpret_cast<const uint4*>(row + 128);
+                        const uint4 a2 = *reinterpret_cast<const uint4*>(row + 256);
+                        ptx::f2 hs[4];
+                        hs[0] = ptx::sum3_bf16x2(a0.x, a1.x, a2.x); hs[1] = ptx::sum3_bf16x2(a0.y, a1.y, a2.y);
+                        hs[2] = ptx::sum3_bf16x2(a0.z, a1.z, a2.z); hs[3] = ptx::sum3_bf16x2(a0.w, a1.w, a2.w);
                         if (j >= 2) {
                             const int orow = r0 + j - 2;
                             ptx::f2 e[4];

@@ -57,6 +57,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     return false;
 }
 
+// Same contract, for the single-lane producer / issuer threads whose wake-up latency sits on the pipeline's
+// critical path: polls with the non-blocking test_wait instead of the suspending try_wait.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* status, int code) {
+    uint64_t t0 = 0;
+    for (uint32_t i = 0; i < WAIT_LIMIT_POLLS; ++i) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 1023u) == 1023u) {
+            if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+            const uint64_t t = globaltimer_ns();
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > WAIT_LIMIT_NS) break;
+        }
+    }
+    atomicCAS(status, 0, code);
+    return false;
+}
+
 // ---- proxies and fences ----------------------------------------------------------------------------------
 // makes this thread's shared-memory writes visible to the async proxy (UMMA operand reads, TMA)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -74,6 +97,12 @@ __device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m
         "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
         ::"r"(smem_u32(smem_dst)), "l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar)) : "memory");
 }
+// hint: bring a 4-D tile / one line into L2 ahead of the load that will need it (no shared memory involved)
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global [%0, {%1, %2, %3, %4}];"
+                 ::"l"((uint64_t)map), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 // TMA store: shared -> global 4-D tile (bulk async group); cells outside the tensor are dropped
 __device__ __forceinline__ void tma_store_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2, int c3) {
     asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
@@ -161,6 +190,23 @@ __device__ __forceinline__ f2 bf16x2_to_f2(uint32_t w) {
     f2 r;
     asm("{\n\t.reg .b32 lo, hi;\n\tshl.b32 lo, %1, 16;\n\tand.b32 hi, %1, 0xffff0000;\n\tmov.b64 %0, {lo, hi};\n\t}" : "=l"(r.v) : "r"(w));
     return r;
+}
+// fp32 + bf16 in one instruction (mixed-precision add): the bf16 operand is the low / high half of a packed word
+__device__ __forceinline__ float add_bf16_lo(uint32_t w, float c) {
+    float d;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tadd.rn.f32.bf16 %0, lo, %2;\n\t}" : "=f"(d) : "r"(w), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float add_bf16_hi(uint32_t w, float c) {
+    float d;
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tadd.rn.f32.bf16 %0, hi, %2;\n\t}" : "=f"(d) : "r"(w), "f"(c));
+    return d;
+}
+// a + b + c of three packed bf16 pairs, in fp32 (one conversion and two mixed adds per lane)
+__device__ __forceinline__ f2 sum3_bf16x2(uint32_t a, uint32_t b, uint32_t c) {
+    const float lo = add_bf16_lo(c, add_bf16_lo(b, __uint_as_float(a << 16)));
+    const float hi = add_bf16_hi(c, add_bf16_hi(b, __uint_as_float(a & 0xffff0000u)));
+    return make_f2(lo, hi);
 }
 __device__ __forceinline__ f2 add2(f2 a, f2 b) { f2 r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
 __device__ __forceinline__ f2 mul2(f2 a, f2 b) { f2 r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r.v) : "l"(a.v), "l"(b.v)); return r; }
