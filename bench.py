@@ -78,11 +78,11 @@ class ClockSampler(threading.Thread):
 
 
 # DRAM bytes per cell-update of each bf16 kernel, from the ncu captures summarised under profiles/
-# (k*_bf16_pipelined_batch8_128x128.txt: dram__bytes_read.sum + dram__bytes_write.sum over 131 072 cells).  The
+# (k1_bf16_batch8_128x128.txt, k2_bf16_batch8_128x128.txt: dram__bytes_read.sum + dram__bytes_write.sum over 131 072 cells).  The
 # capture is a batch of 8 grids (268 MB of E/V per kernel, larger than L2); traffic grows in proportion to the
 # cells, so a full launch is this figure times its cells.  k1's figure sits below its algorithmic bytes because
 # part of what it wrote was still dirty in the 126 MB L2 when the captured launch ended.
-NCU_DRAM_BYTES_PER_CELL = {"k1": (17.312e6 + 227.391e6) / 131072, "k2": (298.444e6 + 13.103e6) / 131072}
+NCU_DRAM_BYTES_PER_CELL = {"k1": (17.489e6 + 226.920e6) / 131072, "k2": (298.092e6 + 13.013e6) / 131072}
 
 
 def cpu_baseline(ca_steps_sample=2, grids=1):
