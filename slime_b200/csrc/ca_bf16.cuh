@@ -214,21 +214,35 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
                 const int r = tn.ty0 + tid / 18 - 1, x = g.wrap_x(tn.tx0 + tid % 18 - 1);
                 ptx::prefetch_l2(X + (size_t)tn.b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC);
             }
-            for (int i = tid; i < 180 * 8; i += 256) {
-                const int q = i & 7, cell = i >> 3;
-                const int hy = cell / 18, hx = cell % 18;
-                const int r = t.ty0 + hy - 1, x = g.wrap_x(t.tx0 + hx - 1);
-                const uint4 raw = *reinterpret_cast<const uint4*>(X + (size_t)t.b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC + q * 8);
+            {
+                // 180 cells x 8 chunks over 256 threads: issue every global load first, then scale and store
+                const int q = tid & 7;                 // constant per thread: 256 is a multiple of 8
                 const float4 s0 = __ldg(reinterpret_cast<const float4*>(sc + q * 8));
                 const float4 s1 = __ldg(reinterpret_cast<const float4*>(sc + q * 8 + 4));
-                float f[8];
-                unpack8(raw, f);
-                f[0] *= s0.x; f[1] *= s0.y; f[2] *= s0.z; f[3] *= s0.w;
-                f[4] *= s1.x; f[5] *= s1.y; f[6] *= s1.z; f[7] *= s1.w;
-                const uint4 v = pack8(f);
-                *reinterpret_cast<uint4*>(xh + cell * 128 + q * 16) = v;
-                if (hy >= 1 && hy <= TBH && hx >= 1 && hx <= TBW)
-                    *reinterpret_cast<uint4*>(a_x + swz((hy - 1) * TBW + hx - 1, q)) = v;
+                uint4 raw[6];
+#pragma unroll
+                for (int n = 0; n < 6; ++n) {
+                    const int cell = (tid >> 3) + n * 32;
+                    if (cell < 180) {
+                        const int r = t.ty0 + cell / 18 - 1, x = g.wrap_x(t.tx0 + cell % 18 - 1);
+                        raw[n] = *reinterpret_cast<const uint4*>(X + (size_t)t.b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC + q * 8);
+                    }
+                }
+#pragma unroll
+                for (int n = 0; n < 6; ++n) {
+                    const int cell = (tid >> 3) + n * 32;
+                    if (cell < 180) {
+                        const int hy = cell / 18, hx = cell % 18;
+                        float f[8];
+                        unpack8(raw[n], f);
+                        f[0] *= s0.x; f[1] *= s0.y; f[2] *= s0.z; f[3] *= s0.w;
+                        f[4] *= s1.x; f[5] *= s1.y; f[6] *= s1.z; f[7] *= s1.w;
+                        const uint4 v = pack8(f);
+                        *reinterpret_cast<uint4*>(xh + cell * 128 + q * 16) = v;
+                        if (hy >= 1 && hy <= TBH && hx >= 1 && hx <= TBW)
+                            *reinterpret_cast<uint4*>(a_x + swz((hy - 1) * TBW + hx - 1, q)) = v;
+                    }
+                }
             }
             ptx::fence_proxy_async();
             ptx::bar_sync(1, 256);
