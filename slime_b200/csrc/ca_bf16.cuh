@@ -309,15 +309,20 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
             // Apron positions that wrap onto this thread's cell (the TMA store below covers the cell itself and
             // whatever hangs over the far edge).  Grids narrower or shorter than twice the apron can wrap more
             // than once and take the general loop.
-            size_t dup_off[3];
-            int ndup = 0;
+            // (kept in named registers, not an indexed array: an array would live in local memory and put a load in
+            // front of every duplicate store)
+            size_t off_x = 0, off_y = 0, off_xy = 0;
+            bool dup_x = false, dup_y = false;
             if (valid_ep && !tiny) {
                 const int xd = x_ep < APRON ? x_ep + g.W : (x_ep >= g.W - APRON ? x_ep - g.W : -100);
                 const int rd = !g.wrap_y ? -100 : (r_ep < APRON ? r_ep + g.H : (r_ep >= g.H - APRON ? r_ep - g.H : -100));
-                if (xd != -100) dup_off[ndup++] = ((size_t)(r_ep + APRON) * g.ev_w + xd + APRON) * HD;
-                if (rd != -100) dup_off[ndup++] = ((size_t)(rd + APRON) * g.ev_w + x_ep + APRON) * HD;
-                if (xd != -100 && rd != -100) dup_off[ndup++] = ((size_t)(rd + APRON) * g.ev_w + xd + APRON) * HD;
+                dup_x = xd != -100;
+                dup_y = rd != -100;
+                if (dup_x) off_x = ((size_t)(r_ep + APRON) * g.ev_w + xd + APRON) * HD;
+                if (dup_y) off_y = ((size_t)(rd + APRON) * g.ev_w + x_ep + APRON) * HD;
+                if (dup_x && dup_y) off_xy = ((size_t)(rd + APRON) * g.ev_w + xd + APRON) * HD;
             }
+            const bool any_dup = valid_ep && (dup_x || dup_y || tiny);
             for (int h = 0; h < NH; ++h) {
                 const int i = k * NH + h, tb = i & 1;
                 const float mu = prm_e[h * PRM + 9], nisl2 = prm_e[h * PRM + 10] * LOG2E;
@@ -362,13 +367,23 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
                     *reinterpret_cast<uint4*>(stg_e + swz(m_ep, qa + 1)) = e_hi;
                     *reinterpret_cast<uint4*>(stg_v + swz(m_ep, qa)) = v_lo;
                     *reinterpret_cast<uint4*>(stg_v + swz(m_ep, qa + 1)) = v_hi;
-                    if (valid_ep && (ndup > 0 || tiny)) {
+                    if (any_dup) {
                         __nv_bfloat16* Eh = E + ((size_t)t.b * NH + h) * eplane + half * 32 + sub * 16;
                         __nv_bfloat16* Vh = V + ((size_t)t.b * NH + h) * eplane + half * 32 + sub * 16;
                         if (!tiny) {
-                            for (int d = 0; d < ndup; ++d) {
-                                uint4* pE = reinterpret_cast<uint4*>(Eh + dup_off[d]);
-                                uint4* pV = reinterpret_cast<uint4*>(Vh + dup_off[d]);
+                            if (dup_x) {
+                                uint4* pE = reinterpret_cast<uint4*>(Eh + off_x);
+                                uint4* pV = reinterpret_cast<uint4*>(Vh + off_x);
+                                pE[0] = e_lo; pE[1] = e_hi; pV[0] = v_lo; pV[1] = v_hi;
+                            }
+                            if (dup_y) {
+                                uint4* pE = reinterpret_cast<uint4*>(Eh + off_y);
+                                uint4* pV = reinterpret_cast<uint4*>(Vh + off_y);
+                                pE[0] = e_lo; pE[1] = e_hi; pV[0] = v_lo; pV[1] = v_hi;
+                            }
+                            if (dup_x && dup_y) {
+                                uint4* pE = reinterpret_cast<uint4*>(Eh + off_xy);
+                                uint4* pV = reinterpret_cast<uint4*>(Vh + off_xy);
                                 pE[0] = e_lo; pE[1] = e_hi; pV[0] = v_lo; pV[1] = v_hi;
                             }
                         } else {
