@@ -31,23 +31,36 @@ constexpr int TBH = 8, TBW = 16;      // tile: 8 rows x 16 columns = 128 cells
 constexpr int APRON = 2;              // apron of the E/V planes, cells
 constexpr float LOG2E = 1.4426950408889634f;
 
+// Tensor maps k1 stores through: the whole 8 x 16 tile, and - for grids made of whole tiles - the pieces whose
+// wrapped copies land at the low end of an apron (a TMA store may hang over the far edge of the tensor, where it
+// is clipped, but must not start before its origin): the tile's last two columns, last two rows and their corner.
+struct K1StoreMaps {
+    CUtensorMap e, v;           // box 64 x 16 x 8 x 1, 128B swizzle
+    CUtensorMap e_col, v_col;   // box 64 x 2 x 8 x 1
+    CUtensorMap e_row, v_row;   // box 64 x 16 x 2 x 1
+    CUtensorMap e_cor, v_cor;   // box 64 x 2 x 2 x 1
+};
+
 struct Bf16Plan {
     int tiles_x = 1, k1_tiles = 1, k2_tiles = 1, k1_grid = 1, k2_grid = 1;
     CUtensorMap map_w1;   // [sets*8*192][64] bf16, box 64 x 192, 128B swizzle
     CUtensorMap map_wo;   // [sets*8*64][64]  bf16, box 64 x 64,  128B swizzle
     CUtensorMap map_e;    // E planes [B*8][H+4][W+4][64], box 64 x 20 x 12 x 1
     CUtensorMap map_v;    // V planes, box 64 x 18 x 10 x 1
-    CUtensorMap map_e_st; // E planes, store box 64 x 16 x 8 x 1, 128B swizzle
-    CUtensorMap map_v_st; // V planes, store box
+    K1StoreMaps st;       // store maps of k1 (whole tile, last two columns, last two rows, their corner)
+    bool k1_aligned = false;
 };
 
 // ---- shared-memory maps (byte offsets from a 1024-aligned base) -------------------------------------------
 namespace k1b {
 constexpr int A_X = 0;                                   // 2 x 16 KB: X operand of the current / next tile
 constexpr int A_CONV = 2 * 16384;                        // 4 x 16 KB: stencil operand slots, two per half
-constexpr int W0 = A_CONV + 4 * 16384, W_STAGE = 24576;  // 3 x 24 KB: Wp|Wi|Wv rows of a head
-constexpr int STG_E = W0 + 3 * W_STAGE, STG_V = STG_E + 16384;   // staging tiles of the TMA stores
-constexpr int XH = STG_V + 16384, XH_BYTES = 10 * 18 * 128;      // state halo tile, plain [10][18] cells x 128 B
+constexpr int W0 = A_CONV + 4 * 16384, W_STAGE = 24576;  // 2 x 24 KB: Wp|Wi|Wv rows of a head
+constexpr int STG_E = W0 + 2 * W_STAGE, STG_V = STG_E + 16384;   // staging tiles of the TMA stores
+constexpr int STG_COL_E = STG_V + 16384, STG_COL_V = STG_COL_E + 2048;   // last two columns  [8][2] cells
+constexpr int STG_ROW_E = STG_COL_V + 2048, STG_ROW_V = STG_ROW_E + 4096; // last two rows     [2][16] cells
+constexpr int STG_COR_E = STG_ROW_V + 4096, STG_COR_V = STG_COR_E + 1024; // their corner      [2][2] cells
+constexpr int XH = STG_COR_V + 1024, XH_BYTES = 10 * 18 * 128;   // state halo tile, plain [10][18] cells x 128 B
 constexpr int PRM_ST = XH + XH_BYTES, PRM_EP = PRM_ST + NH * PRM * 4;   // per-tile copies of the head parameters
 constexpr int BARS = PRM_EP + NH * PRM * 4, TMEM_PTR = BARS + 24 * 8;
 constexpr int BYTES = TMEM_PTR + 16;
@@ -112,19 +125,23 @@ __device__ __forceinline__ CaTile ca_tile(int t, int tiles_per_grid, int tiles_x
 //               4-warp halves take alternate heads: 3x3 stencil marching down columns in packed fp32 -> A operand
 //   warps 8-15  epilogue group: TMEM -> growth bell, E = exp(G*I) -> swizzled staging tiles -> TMA store of the
 //               whole tile (+ register stores of the apron duplicates of edge cells)
-//   warp 16     TMA producer of the per-head weight tiles (3-stage ring)
+//   warp 16     TMA producer of the per-head weight tiles (2-stage ring)
 //   warp 17     UMMA issuer: U (N=64) and I|V (N=128) into a double-buffered 192-column TMEM accumulator
+// ALIGNED: the grid is made of whole tiles (W a multiple of 16, and H a multiple of 8 on a torus), so the wrapped
+// copies of edge cells are whole pieces of a tile and go out as extra TMA stores; otherwise the threads that own
+// edge cells store the copies from registers.
+template <bool ALIGNED>
 __global__ void __launch_bounds__(k1b::THREADS, 1)
-k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUtensorMap map_e_st,
-        const __grid_constant__ CUtensorMap map_v_st, const __nv_bfloat16* __restrict__ X,
+k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1StoreMaps sm_maps,
+        const __nv_bfloat16* __restrict__ X,
         const float* __restrict__ scale, const float* __restrict__ prm, __nv_bfloat16* __restrict__ E,
         __nv_bfloat16* __restrict__ V, int* __restrict__ status, int n_tiles, int tiles_per_grid, Geom g) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = align1024(smem_raw);
     uint64_t* bars = reinterpret_cast<uint64_t*>(sm + k1b::BARS);
     // one waiting party per barrier, observing every phase in turn
-    uint64_t* w_full = bars;            // [3] weight tile of an item landed             (waits: UMMA issuer)
-    uint64_t* w_empty = bars + 3;       // [3] ... and was consumed                      (waits: TMA producer)
+    uint64_t* w_full = bars;            // [2] weight tile of an item landed             (waits: UMMA issuer)
+    uint64_t* w_empty = bars + 3;       // [2] ... and was consumed                      (waits: TMA producer)
     uint64_t* ac_full = bars + 6;       // [4] stencil operand slot written              (waits: UMMA issuer)
     uint64_t* ac_empty = bars + 10;     // [4] ... and consumed                          (waits: the half that owns the slot)
     uint64_t* ax_full = bars + 14;      // [2] X operand of a tile written               (waits: UMMA issuer)
@@ -139,7 +156,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
         ptx::mbar_init(&tm_empty[0], 256);
         ptx::mbar_init(&tm_empty[1], 256);
         ptx::fence_barrier_init();
-        ptx::prefetch_tmap(&map_w1); ptx::prefetch_tmap(&map_e_st); ptx::prefetch_tmap(&map_v_st);
+        ptx::prefetch_tmap(&map_w1); ptx::prefetch_tmap(&sm_maps.e); ptx::prefetch_tmap(&sm_maps.v);
     }
     if (warp == 0) ptx::tmem_alloc(tmem_ptr, k1b::TMEM_COLS);
     ptx::tc_fence_before();
@@ -157,8 +174,8 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
                 const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
                 const int set = t.b / g.per_set;
                 for (int h = 0; h < NH; ++h) {
-                    const int i = k * NH + h, ws = i % 3;
-                    ptx::mbar_wait(&w_empty[ws], ((i / 3) & 1) ^ 1, status, 110);
+                    const int i = k * NH + h, ws = i & 1;
+                    ptx::mbar_wait(&w_empty[ws], ((i >> 1) & 1) ^ 1, status, 110);
                     ptx::mbar_expect_tx(&w_full[ws], k1b::W_STAGE);
                     ptx::tma_load_2d(sm + k1b::W0 + ws * k1b::W_STAGE, &map_w1, 0, (set * NH + h) * 192, &w_full[ws]);
                 }
@@ -172,10 +189,10 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
             for (int k = 0; k < my_tiles; ++k) {
                 const int xb = k & 1;
                 for (int h = 0; h < NH; ++h) {
-                    const int i = k * NH + h, ws = i % 3, half = h & 1, n = k * 4 + (h >> 1);
+                    const int i = k * NH + h, ws = i & 1, half = h & 1, n = k * 4 + (h >> 1);
                     const int slot = half * 2 + (n & 1), tb = i & 1;
                     if (h == 0) ptx::mbar_wait(&ax_full[xb], (k >> 1) & 1, status, 120);
-                    ptx::mbar_wait(&w_full[ws], (i / 3) & 1, status, 121);
+                    ptx::mbar_wait(&w_full[ws], (i >> 1) & 1, status, 121);
                     ptx::mbar_wait(&ac_full[slot], (n >> 1) & 1, status, 122);
                     ptx::mbar_wait(&tm_empty[tb], ((i >> 1) & 1) ^ 1, status, 123);
                     ptx::tc_fence_after();
@@ -307,13 +324,18 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
             if (et < NH * PRM) prm_e[et] = __ldg(prm + (size_t)set * NH * PRM + et);
             ptx::bar_sync(4, 256);
             // Apron positions that wrap onto this thread's cell (the TMA store below covers the cell itself and
-            // whatever hangs over the far edge).  Grids narrower or shorter than twice the apron can wrap more
-            // than once and take the general loop.
-            // (kept in named registers, not an indexed array: an array would live in local memory and put a load in
-            // front of every duplicate store)
+            // whatever hangs over the far edge).
+            const int cy = m_ep >> 4, cx = m_ep & 15;
+            // whole-tile grids: which sides of the grid this tile touches (uniform over the tile)
+            const bool left = t.tx0 == 0, right = t.tx0 + TBW == g.W;
+            const bool top = g.wrap_y && t.ty0 == 0, bottom = g.wrap_y && t.ty0 + TBH == g.H;
+            const bool in_col = right && cx >= TBW - APRON, in_row = bottom && cy >= TBH - APRON;
+            // ragged or tiny grids: per-thread targets (named registers, not an indexed array: an array would live
+            // in local memory and put a load in front of every duplicate store).  Grids narrower or shorter than
+            // twice the apron can wrap more than once and take the general loop.
             size_t off_x = 0, off_y = 0, off_xy = 0;
             bool dup_x = false, dup_y = false;
-            if (valid_ep && !tiny) {
+            if (!ALIGNED && valid_ep && !tiny) {
                 const int xd = x_ep < APRON ? x_ep + g.W : (x_ep >= g.W - APRON ? x_ep - g.W : -100);
                 const int rd = !g.wrap_y ? -100 : (r_ep < APRON ? r_ep + g.H : (r_ep >= g.H - APRON ? r_ep - g.H : -100));
                 dup_x = xd != -100;
@@ -322,7 +344,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
                 if (dup_y) off_y = ((size_t)(rd + APRON) * g.ev_w + x_ep + APRON) * HD;
                 if (dup_x && dup_y) off_xy = ((size_t)(rd + APRON) * g.ev_w + xd + APRON) * HD;
             }
-            const bool any_dup = valid_ep && (dup_x || dup_y || tiny);
+            const bool any_dup = !ALIGNED && valid_ep && (dup_x || dup_y || tiny);
             for (int h = 0; h < NH; ++h) {
                 const int i = k * NH + h, tb = i & 1;
                 const float mu = prm_e[h * PRM + 9], nisl2 = prm_e[h * PRM + 10] * LOG2E;
@@ -367,6 +389,29 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
                     *reinterpret_cast<uint4*>(stg_e + swz(m_ep, qa + 1)) = e_hi;
                     *reinterpret_cast<uint4*>(stg_v + swz(m_ep, qa)) = v_lo;
                     *reinterpret_cast<uint4*>(stg_v + swz(m_ep, qa + 1)) = v_hi;
+                    if (ALIGNED) {
+                        if (in_col) {
+                            const int mc = cy * APRON + cx - (TBW - APRON);
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_COL_E + swz(mc, qa)) = e_lo;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_COL_E + swz(mc, qa + 1)) = e_hi;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_COL_V + swz(mc, qa)) = v_lo;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_COL_V + swz(mc, qa + 1)) = v_hi;
+                        }
+                        if (in_row) {
+                            const int mr = (cy - (TBH - APRON)) * TBW + cx;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_ROW_E + swz(mr, qa)) = e_lo;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_ROW_E + swz(mr, qa + 1)) = e_hi;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_ROW_V + swz(mr, qa)) = v_lo;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_ROW_V + swz(mr, qa + 1)) = v_hi;
+                        }
+                        if (in_col && in_row) {
+                            const int mq = (cy - (TBH - APRON)) * APRON + cx - (TBW - APRON);
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_COR_E + swz(mq, qa)) = e_lo;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_COR_E + swz(mq, qa + 1)) = e_hi;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_COR_V + swz(mq, qa)) = v_lo;
+                            *reinterpret_cast<uint4*>(sm + k1b::STG_COR_V + swz(mq, qa + 1)) = v_hi;
+                        }
+                    }
                     if (any_dup) {
                         __nv_bfloat16* Eh = E + ((size_t)t.b * NH + h) * eplane + half * 32 + sub * 16;
                         __nv_bfloat16* Vh = V + ((size_t)t.b * NH + h) * eplane + half * 32 + sub * 16;
@@ -403,8 +448,38 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ CUte
                 ptx::fence_proxy_async();
                 ptx::bar_sync(4, 256);
                 if (et == 0) {
-                    ptx::tma_store_4d(&map_e_st, stg_e, 0, t.tx0 + APRON, t.ty0 + APRON, t.b * NH + h);
-                    ptx::tma_store_4d(&map_v_st, stg_v, 0, t.tx0 + APRON, t.ty0 + APRON, t.b * NH + h);
+                    const int px = t.tx0 + APRON, py = t.ty0 + APRON, pl = t.b * NH + h;
+                    ptx::tma_store_4d(&sm_maps.e, stg_e, 0, px, py, pl);
+                    ptx::tma_store_4d(&sm_maps.v, stg_v, 0, px, py, pl);
+                    if (ALIGNED) {
+                        // wrapped copies: pieces that land at the high end of an apron are the whole tile stored at the
+                        // shifted position (all but the first two columns / rows are clipped); pieces that land at
+                        // the low end come from the small staging tiles
+                        const int hx = g.W + APRON, hy = g.H + APRON;
+                        if (left) { ptx::tma_store_4d(&sm_maps.e, stg_e, 0, hx, py, pl); ptx::tma_store_4d(&sm_maps.v, stg_v, 0, hx, py, pl); }
+                        if (top) { ptx::tma_store_4d(&sm_maps.e, stg_e, 0, px, hy, pl); ptx::tma_store_4d(&sm_maps.v, stg_v, 0, px, hy, pl); }
+                        if (left && top) { ptx::tma_store_4d(&sm_maps.e, stg_e, 0, hx, hy, pl); ptx::tma_store_4d(&sm_maps.v, stg_v, 0, hx, hy, pl); }
+                        if (right) {
+                            ptx::tma_store_4d(&sm_maps.e_col, sm + k1b::STG_COL_E, 0, 0, py, pl);
+                            ptx::tma_store_4d(&sm_maps.v_col, sm + k1b::STG_COL_V, 0, 0, py, pl);
+                            if (top) {
+                                ptx::tma_store_4d(&sm_maps.e_col, sm + k1b::STG_COL_E, 0, 0, hy, pl);
+                                ptx::tma_store_4d(&sm_maps.v_col, sm + k1b::STG_COL_V, 0, 0, hy, pl);
+                            }
+                        }
+                        if (bottom) {
+                            ptx::tma_store_4d(&sm_maps.e_row, sm + k1b::STG_ROW_E, 0, px, 0, pl);
+                            ptx::tma_store_4d(&sm_maps.v_row, sm + k1b::STG_ROW_V, 0, px, 0, pl);
+                            if (left) {
+                                ptx::tma_store_4d(&sm_maps.e_row, sm + k1b::STG_ROW_E, 0, hx, 0, pl);
+                                ptx::tma_store_4d(&sm_maps.v_row, sm + k1b::STG_ROW_V, 0, hx, 0, pl);
+                            }
+                            if (right) {
+                                ptx::tma_store_4d(&sm_maps.e_cor, sm + k1b::STG_COR_E, 0, 0, 0, pl);
+                                ptx::tma_store_4d(&sm_maps.v_cor, sm + k1b::STG_COR_V, 0, 0, 0, pl);
+                            }
+                        }
+                    }
                     ptx::bulk_commit();
                 }
             }
@@ -735,12 +810,20 @@ inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16*
         return -1;
     }
     if (make_plane_map(enc, &p.map_e, E, g, TBW + 4, TBH + 4) || make_plane_map(enc, &p.map_v, V, g, TBW + 2, TBH + 2) ||
-        make_plane_map(enc, &p.map_e_st, E, g, TBW, TBH, CU_TENSOR_MAP_SWIZZLE_128B) ||
-        make_plane_map(enc, &p.map_v_st, V, g, TBW, TBH, CU_TENSOR_MAP_SWIZZLE_128B)) {
+        make_plane_map(enc, &p.st.e, E, g, TBW, TBH, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        make_plane_map(enc, &p.st.v, V, g, TBW, TBH, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        make_plane_map(enc, &p.st.e_col, E, g, APRON, TBH, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        make_plane_map(enc, &p.st.v_col, V, g, APRON, TBH, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        make_plane_map(enc, &p.st.e_row, E, g, TBW, APRON, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        make_plane_map(enc, &p.st.v_row, V, g, TBW, APRON, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        make_plane_map(enc, &p.st.e_cor, E, g, APRON, APRON, CU_TENSOR_MAP_SWIZZLE_128B) ||
+        make_plane_map(enc, &p.st.v_cor, V, g, APRON, APRON, CU_TENSOR_MAP_SWIZZLE_128B)) {
         bf16_error_ref() = "cuTensorMapEncodeTiled rejected the E/V plane layout";
         return -1;
     }
-    if (cudaFuncSetAttribute(k1_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, k1b::SMEM) != cudaSuccess ||
+    p.k1_aligned = g.W % TBW == 0 && (!g.wrap_y || g.H % TBH == 0);
+    if (cudaFuncSetAttribute(k1_bf16<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, k1b::SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(k1_bf16<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, k1b::SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(k2_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, k2b::SMEM) != cudaSuccess) {
         bf16_error_ref() = "could not opt in to the kernels' dynamic shared memory";
         return -1;
@@ -753,8 +836,12 @@ inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16*
 
 inline int bf16_k1(Bf16Plan& p, const __nv_bfloat16* X, const float* scale, const float* prm, __nv_bfloat16* E,
                    __nv_bfloat16* V, int* status, const Geom& g, cudaStream_t st) {
-    k1_bf16<<<p.k1_grid, k1b::THREADS, k1b::SMEM, st>>>(p.map_w1, p.map_e_st, p.map_v_st, X, scale, prm, E, V, status,
-                                                        p.k1_tiles * g.B, p.k1_tiles, g);
+    if (p.k1_aligned)
+        k1_bf16<true><<<p.k1_grid, k1b::THREADS, k1b::SMEM, st>>>(p.map_w1, p.st, X, scale, prm, E, V, status,
+                                                                  p.k1_tiles * g.B, p.k1_tiles, g);
+    else
+        k1_bf16<false><<<p.k1_grid, k1b::THREADS, k1b::SMEM, st>>>(p.map_w1, p.st, X, scale, prm, E, V, status,
+                                                                   p.k1_tiles * g.B, p.k1_tiles, g);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 
