@@ -347,7 +347,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
             const bool any_dup = !ALIGNED && valid_ep && (dup_x || dup_y || tiny);
             for (int h = 0; h < NH; ++h) {
                 const int i = k * NH + h, tb = i & 1;
-                const float mu = prm_e[h * PRM + 9], nisl2 = prm_e[h * PRM + 10] * LOG2E;
+                const float mus = prm_e[h * PRM + 9];            // mu * s; Wp carries s and Wi carries log2(e)
                 ptx::mbar_wait(&tm_full[tb], (i >> 1) & 1, status, 140);
                 ptx::tc_fence_after();
                 const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16) + tb * 192;
@@ -365,10 +365,9 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                         float e2[2];
 #pragma unroll
                         for (int e = 0; e < 2; ++e) {
-                            const float z = __uint_as_float(ru[2 * j + e]) - mu;
-                            const float gr = fmaf(2.f, ptx::ex2(z * z * nisl2), -1.f);
-                            const float a = fminf(fmaxf(gr * __uint_as_float(ri[2 * j + e]), -80.f), 80.f);
-                            e2[e] = ptx::ex2(a * LOG2E);
+                            const float z = __uint_as_float(ru[2 * j + e]) - mus;
+                            const float gr = fmaf(2.f, ptx::ex2(-(z * z)), -1.f);
+                            e2[e] = ptx::ex2(fminf(fmaxf(gr * __uint_as_float(ri[2 * j + e]), -80.f * LOG2E), 80.f * LOG2E));
                         }
                         pe[sub][j] = pack_bf16(e2[0], e2[1]);
                         pv[sub][j] = pack_bf16(__uint_as_float(rv[2 * j]), __uint_as_float(rv[2 * j + 1]));

@@ -294,6 +294,16 @@ int slime_ca_set_weights(slime_ca* h, int set_index, const float* Wp, const floa
         prm[hd * PRM + 9] = mu[hd];
         prm[hd * PRM + 10] = -1.f / (2.f * sigma[hd] * sigma[hd]);
     }
+    if (is_bf16(h)) {
+        // The bf16 kernels evaluate the growth bell and the softmax numerator in base 2 with the constants folded
+        // into the weights: Wp is scaled by s = sqrt(log2(e) / (2 sigma^2)) and Wi by log2(e), so that
+        // G = 2 exp2(-(U' - mu s)^2) - 1 and E = exp2(G I').  Slot 9 of the parameter block carries mu * s.
+        for (int hd = 0; hd < NH; ++hd) {
+            const float s = sqrtf(1.4426950408889634f / (2.f * sigma[hd] * sigma[hd]));
+            prm[hd * PRM + 9] = mu[hd] * s;
+            prm[hd * PRM + 10] = s;
+        }
+    }
     CK(h, cudaMemcpy(h->prm + (size_t)set_index * NH * PRM, prm.data(), prm.size() * sizeof(float), cudaMemcpyHostToDevice));
     if (is_bf16(h)) {
         // B operands are stored "K-major": one row per output column, the 64 inputs contiguous.
@@ -302,8 +312,8 @@ int slime_ca_set_weights(slime_ca* h, int set_index, const float* Wp, const floa
             for (int c = 0; c < NC; ++c)
                 for (int d = 0; d < HD; ++d) {
                     const size_t src = ((size_t)hd * NC + c) * HD + d;
-                    w1[((size_t)hd * 192 + d) * 64 + c] = __float2bfloat16(Wp[src]);
-                    w1[((size_t)hd * 192 + 64 + d) * 64 + c] = __float2bfloat16(Wi[src]);
+                    w1[((size_t)hd * 192 + d) * 64 + c] = __float2bfloat16(Wp[src] * prm[hd * PRM + 10]);
+                    w1[((size_t)hd * 192 + 64 + d) * 64 + c] = __float2bfloat16(Wi[src] * 1.4426950408889634f);
                     w1[((size_t)hd * 192 + 128 + d) * 64 + c] = __float2bfloat16(Wv[src]);
                     // Wo[(hd*64+d)][c] -> row c (output channel), column d
                     wo[((size_t)hd * 64 + c) * 64 + d] = __float2bfloat16(Wo[((size_t)hd * HD + d) * NC + c]);
