@@ -153,6 +153,31 @@ int slime_ca_lift_images(slime_ca* h, const float* host_img, int img_h, int img_
 int slime_ca_pool_readout(slime_ca* h, const float* host_Wr, const float* host_br, int n_out,
                           float* host_logits, void* stream);
 
+/* The same lift from a DEVICE field [batch][height][width] (fp32) of the grid's own size, as the reference's step
+ * driver does every generation (initialize_ca_from_field_kernel, slime/core/organism.cu:632-636,691-720):
+ * X = field * L[c] with HOST L[64]; the masses become those of the lifted state.  Synchronises `stream`. */
+int slime_ca_lift_field_device(slime_ca* h, const float* dev_field, const float* host_L, void* stream);
+
+/* Write the CA back into a DEVICE field [batch][height][width] (fp32): the mean over the 64 channels of each
+ * cell of the normalised state.  Mirrors update_field_from_ca_kernel (slime/core/organism.cu:723-743).  Enqueued
+ * on `stream`, not synchronised. */
+int slime_ca_field_from_state_device(slime_ca* h, float* dev_field, void* stream);
+
+/*
+ * Upload one weight set straight from the reference's weight bundle (struct MultiHeadCAState,
+ * slime/core/pseudopod.cu:29-38): DEVICE fp32 arrays perception [8][512][256], interaction [8][512][256],
+ * value [8][256][512], head mixing [8][8], flow kernels [8][9].  Taken as the reference's kernels index them:
+ * Wp, Wi = rows c < 64, columns d < 64 of each head's matrix (slime/core/pseudopod.cu:86-87,102-103);
+ * Wv[c][d] = sum over r < 4 of value[c + 64 r][d] (the loop j < 256 with interaction[j % 64], :114-119);
+ * K = flow kernels as stored; Wo[(h, d)][c] = (d == c) * mean over output heads o of mixing[o][h] (the 8 x 8
+ * mixing of :231-249 followed by the mean of the output heads: the bundle has no 512 -> 64 projection).
+ * mu, sigma: HOST [8], or NULL for 0.2 and 0.03 (the bundle carries none).
+ */
+int slime_ca_set_weights_reference_layout(slime_ca* h, int set_index, const float* dev_perception,
+                                          const float* dev_interaction, const float* dev_value,
+                                          const float* dev_head_mixing, const float* dev_flow_kernels,
+                                          const float* mu, const float* sigma);
+
 /* Number of kernels the library has launched on this handle since creation (for launch accounting). */
 long long slime_ca_launch_count(const slime_ca* h);
 

@@ -456,3 +456,48 @@ void oracle_pool_readout(const float* X, int B, int cells, const float* Wr, cons
         }
     }
 }
+
+/*
+ * Write the CA back into a one-channel field: field[b][cell] = mean over the 64 channels of X[b][cell][:].
+ * Follows slime/core/organism.cu:723-743 (update_field_from_ca_kernel: sum over the cell's channels / CHANNELS).
+ */
+void oracle_field_from_state(const float* X, int B, int cells, float* field) {
+    for (size_t i = 0; i < (size_t)B * cells; ++i) {
+        double acc = 0.0;
+        for (int c = 0; c < NC; ++c) acc += (double)X[i * NC + c];
+        field[i] = (float)(acc / NC);
+    }
+}
+
+/*
+ * The contract's weight set taken out of the reference's weight bundle (struct MultiHeadCAState,
+ * slime/core/pseudopod.cu:29-38), as the reference's kernels index it:
+ *   Wp[h][c][d] = perception [h][c][d]  of [8][512][256]   (slime/core/pseudopod.cu:86-87; only c, d < 64 are read)
+ *   Wi[h][c][d] = interaction[h][c][d]  of [8][512][256]   (slime/core/pseudopod.cu:102-103)
+ *   Wv[h][c][d] = sum over r < 4 of value[h][c + 64 r][d] of [8][256][512]: the reference sums j < 256 of
+ *                 interaction[j % 64] * value[h][j][d] (slime/core/pseudopod.cu:114-119)
+ *   K[h][t]     = flow_kernels[h][t]                        (slime/core/pseudopod.cu:153)
+ *   Wo[(h, d)][c] = (d == c) * mean over out-heads o of mixing[o][h]: the 8 x 8 head mixing
+ *                 (slime/core/pseudopod.cu:231-249) followed by the mean of the 8 output heads, which is what a
+ *                 64-channel state can take from a bundle that has no 512 -> 64 projection.
+ */
+void oracle_weights_from_reference_layout(const float* perception, const float* interaction, const float* value,
+                                          const float* mixing, const float* flow, float* Wp, float* Wi, float* Wv,
+                                          float* Wo, float* K) {
+    for (int h = 0; h < NH; ++h) {
+        double m = 0.0;
+        for (int o = 0; o < NH; ++o) m += (double)mixing[o * NH + h];
+        for (int c = 0; c < NC; ++c)
+            for (int d = 0; d < HD; ++d) {
+                const size_t dst = ((size_t)h * NC + c) * HD + d;
+                Wp[dst] = perception[((size_t)h * 512 + c) * 256 + d];
+                Wi[dst] = interaction[((size_t)h * 512 + c) * 256 + d];
+                float acc = 0.f;
+                for (int r = 0; r < 4; ++r) acc += value[((size_t)h * 256 + c + 64 * r) * 512 + d];
+                Wv[dst] = acc;
+                Wo[((size_t)h * HD + d) * NC + c] = d == c ? (float)(m / NH) : 0.f;
+            }
+        for (int t = 0; t < 9; ++t) K[h * 9 + t] = flow[h * 9 + t];
+    }
+}
+

@@ -49,6 +49,10 @@ def _lib(real: str):
         lib.oracle_lift.argtypes = [_F, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _F, _F]
         lib.oracle_pool_readout.restype = None
         lib.oracle_pool_readout.argtypes = [_F, ctypes.c_int, ctypes.c_int, _F, _F, ctypes.c_int, _F]
+        lib.oracle_field_from_state.restype = None
+        lib.oracle_field_from_state.argtypes = [_F, ctypes.c_int, ctypes.c_int, _F]
+        lib.oracle_weights_from_reference_layout.restype = None
+        lib.oracle_weights_from_reference_layout.argtypes = [_F] * 10
         _LIBS[real] = lib
     return _LIBS[real]
 
@@ -141,3 +145,21 @@ def pool_readout(X, Wr, br):
     out = np.zeros((B, n_out), np.float32)
     _lib("f64").oracle_pool_readout(_f(X), B, cells, _f(Wr), _f(None if br is None else _c32(br)), n_out, _f(out))
     return out
+
+
+def field_from_state(X):
+    """field[b, y, x] = mean over channels of X[b, y, x, :]."""
+    X = _c32(X)
+    out = np.zeros(X.shape[:-1], np.float32)
+    _lib("f64").oracle_field_from_state(_f(X), X.shape[0], int(np.prod(X.shape[1:-1])), _f(out))
+    return out
+
+
+def weights_from_reference_layout(perception, interaction, value, mixing, flow):
+    """Contract weight arrays (Wp, Wi, Wv, Wo, K) from the reference's bundle layouts
+    ([8][512][256], [8][512][256], [8][256][512], [8][8], [8][9])."""
+    Wp = np.zeros((8, 64, 64), np.float32); Wi = np.zeros_like(Wp); Wv = np.zeros_like(Wp)
+    Wo = np.zeros((512, 64), np.float32); K = np.zeros((8, 9), np.float32)
+    _lib("f64").oracle_weights_from_reference_layout(_f(_c32(perception)), _f(_c32(interaction)), _f(_c32(value)),
+                                                    _f(_c32(mixing)), _f(_c32(flow)), _f(Wp), _f(Wi), _f(Wv), _f(Wo), _f(K))
+    return Wp, Wi, Wv, Wo, K

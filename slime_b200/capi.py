@@ -25,6 +25,7 @@ SYMBOLS = (
     "slime_ca_step_partial", "slime_ca_step_finish", "slime_ca_step_timed", "slime_ca_buffer", "slime_ca_fitness",
     "slime_ca_lift_images", "slime_ca_pool_readout", "slime_ca_launch_count", "launch_multi_head_ca",
     "slime_ca_channel_sums_static", "slime_ca_static_error",
+    "slime_ca_lift_field_device", "slime_ca_field_from_state_device", "slime_ca_set_weights_reference_layout",
 )
 
 
@@ -72,6 +73,9 @@ def lib():
         L.slime_ca_fitness.argtypes = [vp, fp, fp, fp, fp, vp]
         L.slime_ca_lift_images.argtypes = [vp, fp, ctypes.c_int, ctypes.c_int, fp, vp]
         L.slime_ca_pool_readout.argtypes = [vp, fp, fp, ctypes.c_int, fp, vp]
+        L.slime_ca_lift_field_device.argtypes = [vp, vp, fp, vp]
+        L.slime_ca_field_from_state_device.argtypes = [vp, vp, vp]
+        L.slime_ca_set_weights_reference_layout.argtypes = [vp, ctypes.c_int] + [vp] * 5 + [fp, fp]
         L.slime_ca_launch_count.argtypes = [vp]
         L.slime_ca_launch_count.restype = ctypes.c_longlong
         L.launch_multi_head_ca.argtypes = [vp, vp, vp, ctypes.c_int, ctypes.c_int]
@@ -218,6 +222,25 @@ class Handle:
         img, L = _f32(img), _f32(L)
         assert img.shape[0] == self.cfg.batch and L.shape == (64,)
         self._ck(lib().slime_ca_lift_images(self._h, _fp(img), img.shape[1], img.shape[2], _fp(L), stream))
+
+    def lift_field_device(self, dev_field_ptr, L, stream=0):
+        """Lift a device field [batch][height][width] fp32 (raw address) into the state."""
+        L = _f32(L)
+        assert L.shape == (64,)
+        self._ck(lib().slime_ca_lift_field_device(self._h, dev_field_ptr, _fp(L), stream))
+
+    def field_from_state_device(self, dev_field_ptr, stream=0):
+        """Mean over channels of the normalised state into a device field [batch][height][width] fp32."""
+        self._ck(lib().slime_ca_field_from_state_device(self._h, dev_field_ptr, stream))
+
+    def set_weights_reference_layout(self, perception_ptr, interaction_ptr, value_ptr, mixing_ptr, flow_ptr,
+                                     mu=None, sigma=None, set_index=0):
+        """Upload a weight set from device arrays in the reference bundle's layouts (raw addresses)."""
+        m = None if mu is None else _f32(mu)
+        s = None if sigma is None else _f32(sigma)
+        self._ck(lib().slime_ca_set_weights_reference_layout(
+            self._h, set_index, perception_ptr, interaction_ptr, value_ptr, mixing_ptr, flow_ptr,
+            None if m is None else _fp(m), None if s is None else _fp(s)))
 
     def pool_readout(self, Wr, br=None, stream=0):
         Wr = _f32(Wr)

@@ -111,6 +111,31 @@ __global__ void k_lift(const float* __restrict__ img, int ih, int iw, const floa
     }
 }
 
+// field[b][cell] = mean over the 64 channels of the normalised state (stored value x pending scale).  Eight
+// threads per cell, eight channels each, summed by a fixed shuffle tree.
+template <typename T>
+__global__ void __launch_bounds__(256)
+k_channel_mean(const T* __restrict__ X, const float* __restrict__ scale, float* __restrict__ field, Geom g) {
+    const size_t cells = (size_t)g.H * g.W, n = cells * g.B;
+    const int q = threadIdx.x & 7;
+    // a warp covers 4 consecutive cells; the loop condition is on the warp's first cell, so all 32 lanes shuffle
+    for (size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) >> 3; (i & ~size_t(3)) < n;
+         i += ((size_t)gridDim.x * blockDim.x) >> 3) {
+        float s = 0.f;
+        const bool live = i < n;
+        const size_t b = live ? i / cells : 0, cell = live ? i % cells : 0;
+        if (live) {
+            const T* px = X + ((b * g.state_rows() + g.hx) * g.W) * NC + cell * NC + q * 8;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) s = fmaf(to_f32<T>(px[k]), scale[b * NC + q * 8 + k], s);
+        }
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (live && q == 0) field[i] = s * (1.f / NC);
+    }
+}
+
 // logits[b][o] = sum_c (sums[b][c] * scale[b][c] / cells) Wr[c][o] + br[o]
 __global__ void k_pool_readout(const double* __restrict__ sums, const float* __restrict__ scale, double inv_cells,
                                const float* __restrict__ Wr, const float* __restrict__ br, int n_out,

@@ -591,6 +591,77 @@ int slime_ca_pool_readout(slime_ca* h, const float* host_Wr, const float* host_b
     return SLIME_CA_OK;
 }
 
+int slime_ca_lift_field_device(slime_ca* h, const float* dev_field, const float* host_L, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!dev_field || !host_L) return fail(h, SLIME_CA_EINVAL, "null field or lift vector");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const Geom& g = h->g;
+    float* d_L = (float*)h->V;
+    CK(h, cudaMemcpyAsync(d_L, host_L, NC * sizeof(float), cudaMemcpyHostToDevice, st));
+    const int blocks = grid_for((size_t)g.B * g.H * g.W * NC);
+    if (is_bf16(h)) k_lift<__nv_bfloat16><<<blocks, 256, 0, st>>>(dev_field, g.H, g.W, d_L, (__nv_bfloat16*)h->X, g);
+    else k_lift<float><<<blocks, 256, 0, st>>>(dev_field, g.H, g.W, d_L, (float*)h->X, g);
+    LAUNCHED(h);
+    int rc = channel_sums(h, 1, st);
+    if (rc) return rc;
+    CK(h, cudaStreamSynchronize(st));
+    h->state_set = true;
+    h->vp_steps = 0;
+    return SLIME_CA_OK;
+}
+
+int slime_ca_field_from_state_device(slime_ca* h, float* dev_field, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!dev_field) return fail(h, SLIME_CA_EINVAL, "null field");
+    if (!h->state_set) return fail(h, SLIME_CA_ESTATE, "no state has been loaded");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const Geom& g = h->g;
+    const int blocks = grid_for((size_t)g.B * g.H * g.W * 8);
+    if (is_bf16(h)) k_channel_mean<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)h->X, h->scale, dev_field, g);
+    else k_channel_mean<float><<<blocks, 256, 0, st>>>((const float*)h->X, h->scale, dev_field, g);
+    LAUNCHED(h);
+    return SLIME_CA_OK;
+}
+
+int slime_ca_set_weights_reference_layout(slime_ca* h, int set_index, const float* dev_perception,
+                                          const float* dev_interaction, const float* dev_value,
+                                          const float* dev_head_mixing, const float* dev_flow_kernels,
+                                          const float* mu, const float* sigma) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!dev_perception || !dev_interaction || !dev_value || !dev_head_mixing || !dev_flow_kernels)
+        return fail(h, SLIME_CA_EINVAL, "null weight pointer");
+    CK(h, cudaSetDevice(h->cfg.device));
+    // Only the slices the reference's kernels index are fetched: rows c < 64, columns d < 64 of each head's
+    // [512][256] perception / interaction matrix, and columns d < 64 of all 256 rows of the [256][512] value matrix.
+    std::vector<float> Wp((size_t)NH * NC * HD), Wi(Wp.size()), Wv(Wp.size()), Wo((size_t)NH * HD * NC, 0.f);
+    std::vector<float> val((size_t)256 * HD), mix(NH * NH), K(NH * 9), mu_d(NH, 0.2f), sg_d(NH, 0.03f);
+    for (int hd = 0; hd < NH; ++hd) {
+        CK(h, cudaMemcpy2D(&Wp[(size_t)hd * NC * HD], HD * sizeof(float), dev_perception + (size_t)hd * 512 * 256,
+                           256 * sizeof(float), HD * sizeof(float), NC, cudaMemcpyDeviceToHost));
+        CK(h, cudaMemcpy2D(&Wi[(size_t)hd * NC * HD], HD * sizeof(float), dev_interaction + (size_t)hd * 512 * 256,
+                           256 * sizeof(float), HD * sizeof(float), NC, cudaMemcpyDeviceToHost));
+        CK(h, cudaMemcpy2D(val.data(), HD * sizeof(float), dev_value + (size_t)hd * 256 * 512, 512 * sizeof(float),
+                           HD * sizeof(float), 256, cudaMemcpyDeviceToHost));
+        for (int c = 0; c < NC; ++c)
+            for (int d = 0; d < HD; ++d) {
+                float acc = 0.f;     // the reference reads value row j with interaction[j % 64], j < 256
+                for (int r = 0; r < 4; ++r) acc += val[(size_t)(c + 64 * r) * HD + d];
+                Wv[((size_t)hd * NC + c) * HD + d] = acc;
+            }
+    }
+    CK(h, cudaMemcpy(mix.data(), dev_head_mixing, mix.size() * sizeof(float), cudaMemcpyDeviceToHost));
+    CK(h, cudaMemcpy(K.data(), dev_flow_kernels, K.size() * sizeof(float), cudaMemcpyDeviceToHost));
+    for (int hd = 0; hd < NH; ++hd) {
+        double m = 0.0;              // head mixing followed by the mean of the 8 output heads
+        for (int o = 0; o < NH; ++o) m += (double)mix[o * NH + hd];
+        for (int d = 0; d < HD; ++d) Wo[((size_t)hd * HD + d) * NC + d] = (float)(m / NH);
+    }
+    return slime_ca_set_weights(h, set_index, Wp.data(), Wi.data(), Wv.data(), Wo.data(), K.data(),
+                                mu ? mu : mu_d.data(), sigma ? sigma : sg_d.data());
+}
+
 void launch_multi_head_ca(float* ca_state, float* weights, float* ca_output, int batch_size, int grid_size) {
     static slime_ca* cached = nullptr;
     if (!ca_state || !weights || !ca_output || batch_size <= 0 || grid_size <= 0) {

@@ -1,0 +1,66 @@
+"""The source-level stand-in for the reference's slime/core/pseudopod.cu (include/compat/pseudopod.cu): it
+compiles on its own, the reference's translation unit compiles unchanged against it (when a checkout of the
+reference sits beside this repository), and the oracle's reading of the reference's weight bundle is what plain
+slicing gives."""
+import os
+import shutil
+import subprocess
+
+import numpy as np
+import pytest
+
+from oracle import ca_oracle
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+REFERENCE = os.environ.get("SLIME_REFERENCE_ROOT", os.path.join(os.path.dirname(ROOT), "reference"))
+FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-rdc=true", "--expt-relaxed-constexpr", "-w"]
+
+
+def _env():
+    env = dict(os.environ)
+    env.pop("CC", None); env.pop("CXX", None)
+    return env
+
+
+@pytest.mark.skipif(not os.path.exists(NVCC), reason="needs nvcc")
+def test_compat_file_compiles_alone(tmp_path):
+    src = tmp_path / "tu.cu"
+    src.write_text('#include "compat/pseudopod.cu"\nint main() { return 0; }\n')
+    subprocess.run([NVCC, *FLAGS, "-I" + os.path.join(ROOT, "include"), "-c", str(src), "-o", str(tmp_path / "tu.o")],
+                   check=True, env=_env())
+
+
+@pytest.mark.skipif(not os.path.exists(NVCC) or not os.path.exists(os.path.join(REFERENCE, "slime", "core", "organism.cu")),
+                    reason="needs nvcc and a checkout of the reference beside this repository")
+def test_reference_translation_unit_compiles_against_compat(tmp_path):
+    """main.cu -> runtime.cu -> organism.cu, all unchanged, with only core/pseudopod.cu swapped (in a scratch copy)."""
+    shutil.copy(os.path.join(REFERENCE, "main.cu"), tmp_path / "main.cu")
+    shutil.copytree(os.path.join(REFERENCE, "slime"), tmp_path / "slime")
+    shutil.copy(os.path.join(ROOT, "include", "compat", "pseudopod.cu"), tmp_path / "slime" / "core" / "pseudopod.cu")
+    subprocess.run([NVCC, *FLAGS, "-I" + str(tmp_path), "-I" + os.path.join(ROOT, "include"), "-c",
+                    str(tmp_path / "main.cu"), "-o", str(tmp_path / "main.o")], check=True, env=_env())
+    assert os.path.getsize(tmp_path / "main.o") > 0
+
+
+def test_oracle_weights_from_reference_layout():
+    rng = np.random.default_rng(3)
+    per = rng.standard_normal((8, 512, 256)).astype(np.float32)
+    inter = rng.standard_normal((8, 512, 256)).astype(np.float32)
+    val = rng.standard_normal((8, 256, 512)).astype(np.float32)
+    mix = (np.eye(8) + 0.01 * rng.standard_normal((8, 8))).astype(np.float32)
+    flow = rng.random((8, 9)).astype(np.float32)
+    Wp, Wi, Wv, Wo, K = ca_oracle.weights_from_reference_layout(per, inter, val, mix, flow)
+    assert np.array_equal(Wp, per[:, :64, :64]) and np.array_equal(Wi, inter[:, :64, :64])
+    folded = ((val[:, 0:64, :64] + val[:, 64:128, :64]) + val[:, 128:192, :64]) + val[:, 192:256, :64]
+    assert np.array_equal(Wv, folded)
+    assert np.array_equal(K, flow)
+    Wo4 = Wo.reshape(8, 64, 64)
+    for h in range(8):
+        assert np.allclose(Wo4[h], np.eye(64) * mix[:, h].astype(np.float64).mean(), atol=1e-7)
+
+
+def test_oracle_field_from_state():
+    rng = np.random.default_rng(4)
+    X = rng.random((2, 5, 7, 64)).astype(np.float32)
+    assert np.allclose(ca_oracle.field_from_state(X), X.astype(np.float64).mean(-1), atol=1e-7)

@@ -1,0 +1,104 @@
+"""The reference-facing side of the boundary on a GPU: weights taken straight from the reference's device-side
+bundle layouts, the field lift / write-back of the reference's step driver, and the source-level stand-in for
+slime/core/pseudopod.cu driven by a small CUDA program."""
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def build_compat_test():
+    from slime_b200 import build
+    lib = build.build()
+    exe = os.path.join(ROOT, "tests", "cpp", "test_compat")
+    src = os.path.join(ROOT, "tests", "cpp", "test_compat.cu")
+    deps = [src, lib, os.path.join(ROOT, "include", "compat", "pseudopod.cu"), os.path.join(ROOT, "include", "slime_ca.h")]
+    if not os.path.exists(exe) or os.path.getmtime(exe) < max(os.path.getmtime(d) for d in deps):
+        env = dict(os.environ)
+        env.pop("CC", None); env.pop("CXX", None)
+        subprocess.run([os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc"), "-gencode", "arch=compute_100a,code=sm_100a",
+                        "-std=c++17", "--expt-relaxed-constexpr", "-w", "-I" + os.path.join(ROOT, "include"), "-o", exe, src,
+                        "-L" + os.path.dirname(lib), "-lslime_ca", "-Xlinker", "-rpath", "-Xlinker", os.path.dirname(lib)],
+                       check=True, env=env)
+    return exe
+
+
+def test_compat_pseudopod_program():
+    exe = build_compat_test()
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert out.stdout.strip().endswith("ok")
+
+
+@pytest.mark.parametrize("dtype_name", ["f32", "bf16"])
+def test_weights_from_reference_layout_match_host_slicing(dtype_name):
+    import torch
+    from oracle import ca_oracle
+    from slime_b200 import capi, inputs
+    dt = capi.F32 if dtype_name == "f32" else capi.BF16
+    rng = np.random.default_rng(11)
+    per = (rng.standard_normal((8, 512, 256)) * 0.125).astype(np.float32)
+    inter = (rng.standard_normal((8, 512, 256)) * 0.125).astype(np.float32)
+    val = (rng.standard_normal((8, 256, 512)) * 0.0625).astype(np.float32)
+    mix = (np.eye(8) + 0.01 * rng.standard_normal((8, 8))).astype(np.float32)
+    flow = rng.random((8, 9)).astype(np.float32)
+    flow /= flow.sum(1, keepdims=True)
+    mu = np.full(8, 0.2, np.float32); sigma = np.full(8, 0.03, np.float32)
+    dev = [torch.from_numpy(a).cuda() for a in (per, inter, val, mix, flow)]
+    X0 = inputs.make_state(2, 16, 32, seed=5, scale=0.45 * 16 * 32)
+    Wp, Wi, Wv, Wo, K = ca_oracle.weights_from_reference_layout(per, inter, val, mix, flow)
+    with capi.Handle(2, 16, 32, dtype=dt) as a, capi.Handle(2, 16, 32, dtype=dt) as b:
+        a.set_weights_reference_layout(*[t.data_ptr() for t in dev])            # mu, sigma default to 0.2, 0.03
+        b.set_weights(inputs.WeightSets(Wp[None], Wi[None], Wv[None], Wo[None], K[None], mu[None], sigma[None]))
+        for h in (a, b):
+            h.set_state(X0)
+            h.step(2)
+        assert np.array_equal(a.get_state(), b.get_state())
+    # and the f32 path agrees with the oracle run on the oracle's reading of the bundle
+    if dtype_name == "f32":
+        w = inputs.WeightSets(Wp[None], Wi[None], Wv[None], Wo[None], K[None], mu[None], sigma[None])
+        ref = ca_oracle.ca_steps(X0, w, 2, literal=False)
+        with capi.Handle(2, 16, 32, dtype=dt) as a:
+            a.set_weights_reference_layout(*[t.data_ptr() for t in dev])
+            a.set_state(X0)
+            a.step(2)
+            got = a.get_state()
+        assert np.linalg.norm(got - ref) / np.linalg.norm(ref) < 1e-5
+
+
+@pytest.mark.parametrize("dtype_name,tol", [("f32", 1e-6), ("bf16", 1e-2)])
+def test_field_lift_and_write_back(dtype_name, tol):
+    import torch
+    from oracle import ca_oracle
+    from slime_b200 import capi, inputs
+    dt = capi.F32 if dtype_name == "f32" else capi.BF16
+    B, H, W = 3, 24, 40
+    rng = np.random.default_rng(2)
+    field = (0.25 + 0.5 * rng.random((B, H, W))).astype(np.float32)
+    L, _, _ = inputs.make_lift_readout(seed=9)
+    w = inputs.make_weight_sets(1, seed=42)
+    d_field = torch.from_numpy(field).cuda()
+    d_out = torch.zeros_like(d_field)
+    with capi.Handle(B, H, W, dtype=dt) as h:
+        h.set_weights(w)
+        h.lift_field_device(d_field.data_ptr(), L)
+        X0 = h.get_state()
+        ref0 = ca_oracle.lift(field, L, 0)
+        assert np.linalg.norm(X0 - ref0) / np.linalg.norm(ref0) < (1e-7 if dtype_name == "f32" else 4e-3)
+        h.field_from_state_device(d_out.data_ptr())
+        torch.cuda.synchronize()
+        assert np.abs(d_out.cpu().numpy() - ca_oracle.field_from_state(X0)).max() < 1e-6 * np.abs(X0).max() + 1e-7
+        h.step(2)
+        h.field_from_state_device(d_out.data_ptr())
+        torch.cuda.synchronize()
+        got = d_out.cpu().numpy()
+        # against the oracle's trajectory from the state the device actually holds after the lift
+        ref = ca_oracle.field_from_state(ca_oracle.ca_steps(X0, w, 2, literal=False).astype(np.float32))
+        assert np.linalg.norm(got - ref) / np.linalg.norm(ref) < tol
+        # and the channel mean of what get_state returns, up to summation order
+        assert np.abs(got - ca_oracle.field_from_state(h.get_state())).max() < 2e-6 * np.abs(got).max() + 1e-7
