@@ -141,6 +141,38 @@ int slime_ca_buffer(slime_ca* h, int which, void** dev_ptr, size_t* bytes);
  */
 int slime_ca_fitness(slime_ca* h, float* rank, float* coherence, float* fitness, float* hunger, void* stream);
 
+/* Read one weight set back (HOST fp32 arrays in the layouts of slime_ca_set_weights; any may be NULL): the
+ * device-resident master copy, i.e. what was uploaded or what the population step made of it. */
+int slime_ca_get_weights(slime_ca* h, int set_index, float* Wp, float* Wi, float* Wv, float* Wo, float* K, float* mu,
+                         float* sigma);
+
+/*
+ * The population step that consumes the fitness scalars, on the device: replaces culling_kernel,
+ * selection_kernel's search for the best, and spawn_wave_kernel / spawn_component_kernel
+ * (slime/core/organism.cu:430-470,556-614; slime/memory/pool.cu:57-121) for a population of weight sets.
+ *   fitness, hunger of a weight set = mean over its grids of the values slime_ca_fitness last computed;
+ *   culled  : fitness < 0.1 * fitness_threshold, or hunger > hunger_threshold, or not finite
+ *             (slime/core/organism.cu:594-611);
+ *   best    : highest fitness among the survivors, lowest index on ties (slime/core/organism.cu:442-470);
+ *   refill  : every culled set becomes a copy of the best whose Wp, Wi, Wv, Wo values are each perturbed with
+ *             probability mutation_rate by mutation_sigma * N(0, 1) (slime/memory/pool.cu:84-93; the driver
+ *             uses rate 0.01, slime/core/organism.cu:578); taps, mu and sigma are inherited unchanged.  If no
+ *             set survives nothing changes.
+ * The draws depend only on (seed, generation, set index, value index).  Must follow slime_ca_fitness on the same
+ * state.  parent: HOST [n_weight_sets] or NULL, parent[s] = s for survivors, the best set for replaced ones;
+ * best_set (-1 if none survived) and n_replaced may be NULL.  Synchronises `stream`.
+ */
+typedef struct slime_ca_evolve_params {
+    float fitness_threshold;
+    float hunger_threshold;
+    float mutation_rate;
+    float mutation_sigma;
+    unsigned long long seed;
+    int generation;
+} slime_ca_evolve_params;
+int slime_ca_evolve(slime_ca* h, const slime_ca_evolve_params* p, int* parent, int* best_set, int* n_replaced,
+                    void* stream);
+
 /* Lift a one-channel HOST image batch [batch][img_h][img_w] (fp32) into the state: zero-pad to
  * height x width (centred), X = pixel * L[c].  Mirrors initialize_ca_from_field_kernel
  * (slime/core/organism.cu:691-720). */

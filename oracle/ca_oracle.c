@@ -501,3 +501,68 @@ void oracle_weights_from_reference_layout(const float* perception, const float* 
     }
 }
 
+/*
+ * The population step over weight sets (culling, best, refill by mutated copies of the best).  Rules:
+ * culling thresholds slime/core/organism.cu:594-611; best = arg max fitness, slime/core/organism.cu:442-470;
+ * refill = parent's values, each perturbed with probability `rate` by sigma * N(0,1), slime/memory/pool.cu:84-93.
+ * fit: [n_sets * per_set][4] = {rank, coherence, fitness, hunger} per grid.  Wp, Wi, Wv: [n_sets][8*64*64],
+ * Wo: [n_sets][512*64], updated in place.  parent[s] = s for survivors, else the best; returns the number of
+ * replaced sets and stores the best index (or -1).  The perturbation stream is a counter hash of
+ * (seed, generation, set, value index, draw).
+ */
+static uint64_t evolve_mix(uint64_t z) {
+    z += 0x9e3779b97f4a7c15ull;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return z ^ (z >> 31);
+}
+static uint32_t evolve_bits(uint64_t seed, int generation, int s, int i, int k) {
+    const uint64_t key = evolve_mix(evolve_mix(seed ^ ((uint64_t)(uint32_t)generation << 32)) ^ (uint64_t)(uint32_t)s);
+    return (uint32_t)(evolve_mix(key ^ ((uint64_t)(uint32_t)i * 4u + (uint32_t)k)) >> 40);
+}
+int oracle_evolve(const float* fit, int n_sets, int per_set, float fitness_threshold, float hunger_threshold,
+                  float rate, float sigma, unsigned long long seed, int generation, float* Wp, float* Wi, float* Wv,
+                  float* Wo, int* parent, int* best_out) {
+    const int NM = NH * NC * HD;
+    float* mf = (float*)malloc(sizeof(float) * (size_t)n_sets);
+    int best = -1, replaced = 0;
+    for (int s = 0; s < n_sets; ++s) {
+        double f = 0.0, q = 0.0;
+        for (int j = 0; j < per_set; ++j) {
+            f += (double)fit[(size_t)(s * per_set + j) * 4 + 2];
+            q += (double)fit[(size_t)(s * per_set + j) * 4 + 3];
+        }
+        mf[s] = (float)(f / per_set);
+        const float mq = (float)(q / per_set);
+        const int alive = isfinite(mf[s]) && isfinite(mq) && !(mf[s] < 0.1f * fitness_threshold) && !(mq > hunger_threshold);
+        parent[s] = alive ? s : -1;
+        if (!alive) { ++replaced; continue; }
+        if (best < 0 || mf[s] > mf[best]) best = s;
+    }
+    free(mf);
+    *best_out = best;
+    if (best < 0) {
+        for (int s = 0; s < n_sets; ++s) parent[s] = s;
+        return 0;
+    }
+    float r = rate < 0.f ? 0.f : (rate > 1.f ? 1.f : rate);
+    const uint32_t rate24 = (uint32_t)(r * 16777216.0f);
+    float* arrays[4] = { Wp, Wi, Wv, Wo };
+    for (int s = 0; s < n_sets; ++s) {
+        if (parent[s] >= 0) continue;
+        parent[s] = best;
+        for (int a = 0; a < 4; ++a)
+            for (int j = 0; j < NM; ++j) {
+                const int i = a * NM + j;       /* index in the set's concatenated Wp | Wi | Wv | Wo */
+                double v = (double)arrays[a][(size_t)best * NM + j];
+                if (evolve_bits(seed, generation, s, i, 0) < rate24) {
+                    const double u1 = ((double)evolve_bits(seed, generation, s, i, 1) + 1.0) / 16777216.0;
+                    const double u2 = (double)evolve_bits(seed, generation, s, i, 2) / 16777216.0;
+                    v = (double)(float)v + (double)sigma * sqrt(-2.0 * log(u1)) * cos(6.283185307179586 * u2);
+                }
+                arrays[a][(size_t)s * NM + j] = (float)v;
+            }
+    }
+    return replaced;
+}
+

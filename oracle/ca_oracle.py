@@ -53,6 +53,10 @@ def _lib(real: str):
         lib.oracle_field_from_state.argtypes = [_F, ctypes.c_int, ctypes.c_int, _F]
         lib.oracle_weights_from_reference_layout.restype = None
         lib.oracle_weights_from_reference_layout.argtypes = [_F] * 10
+        lib.oracle_evolve.restype = ctypes.c_int
+        lib.oracle_evolve.argtypes = [_F, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float,
+                                      ctypes.c_float, ctypes.c_ulonglong, ctypes.c_int, _F, _F, _F, _F,
+                                      ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]
         _LIBS[real] = lib
     return _LIBS[real]
 
@@ -163,3 +167,20 @@ def weights_from_reference_layout(perception, interaction, value, mixing, flow):
     _lib("f64").oracle_weights_from_reference_layout(_f(_c32(perception)), _f(_c32(interaction)), _f(_c32(value)),
                                                     _f(_c32(mixing)), _f(_c32(flow)), _f(Wp), _f(Wi), _f(Wv), _f(Wo), _f(K))
     return Wp, Wi, Wv, Wo, K
+
+
+def evolve(fit, weights, per_set, *, fitness_threshold, hunger_threshold, mutation_rate, mutation_sigma, seed,
+           generation):
+    """The population step.  fit: [n_grids, 4] = rank, coherence, fitness, hunger per grid; weights: an object with
+    arrays() -> (Wp, Wi, Wv, Wo, K, mu, sigma) stacked over sets.  Returns (new arrays tuple, parent, best, n_replaced)."""
+    Wp, Wi, Wv, Wo, K, mu, sigma = [np.array(a, dtype=np.float32, order="C", copy=True) for a in weights.arrays()]
+    n_sets = Wp.shape[0]
+    fit = _c32(fit)
+    assert fit.shape == (n_sets * per_set, 4)
+    parent = np.zeros(n_sets, np.int32)
+    best = ctypes.c_int(-1)
+    n = _lib("f64").oracle_evolve(_f(fit), n_sets, per_set, fitness_threshold, hunger_threshold, mutation_rate,
+                                  mutation_sigma, seed, generation, _f(Wp), _f(Wi), _f(Wv), _f(Wo),
+                                  parent.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), ctypes.byref(best))
+    K, mu, sigma = K[parent], mu[parent], sigma[parent]      # taps, mu and sigma are inherited unchanged
+    return (Wp, Wi, Wv, Wo, K, mu, sigma), parent, best.value, n

@@ -26,6 +26,7 @@ SYMBOLS = (
     "slime_ca_lift_images", "slime_ca_pool_readout", "slime_ca_launch_count", "launch_multi_head_ca",
     "slime_ca_channel_sums_static", "slime_ca_static_error",
     "slime_ca_lift_field_device", "slime_ca_field_from_state_device", "slime_ca_set_weights_reference_layout",
+    "slime_ca_get_weights", "slime_ca_evolve",
 )
 
 
@@ -39,6 +40,12 @@ class Config(ctypes.Structure):
     _fields_ = [("batch", ctypes.c_int), ("height", ctypes.c_int), ("width", ctypes.c_int),
                 ("n_weight_sets", ctypes.c_int), ("dtype", ctypes.c_int), ("dt", ctypes.c_float),
                 ("device", ctypes.c_int), ("stripe", ctypes.c_int), ("keep_vprime", ctypes.c_int)]
+
+
+class EvolveParams(ctypes.Structure):
+    _fields_ = [("fitness_threshold", ctypes.c_float), ("hunger_threshold", ctypes.c_float),
+                ("mutation_rate", ctypes.c_float), ("mutation_sigma", ctypes.c_float),
+                ("seed", ctypes.c_ulonglong), ("generation", ctypes.c_int)]
 
 
 _lib = None
@@ -76,6 +83,9 @@ def lib():
         L.slime_ca_lift_field_device.argtypes = [vp, vp, fp, vp]
         L.slime_ca_field_from_state_device.argtypes = [vp, vp, vp]
         L.slime_ca_set_weights_reference_layout.argtypes = [vp, ctypes.c_int] + [vp] * 5 + [fp, fp]
+        L.slime_ca_get_weights.argtypes = [vp, ctypes.c_int] + [fp] * 7
+        ip = ctypes.POINTER(ctypes.c_int)
+        L.slime_ca_evolve.argtypes = [vp, ctypes.POINTER(EvolveParams), ip, ip, ip, vp]
         L.slime_ca_launch_count.argtypes = [vp]
         L.slime_ca_launch_count.restype = ctypes.c_longlong
         L.launch_multi_head_ca.argtypes = [vp, vp, vp, ctypes.c_int, ctypes.c_int]
@@ -241,6 +251,22 @@ class Handle:
         self._ck(lib().slime_ca_set_weights_reference_layout(
             self._h, set_index, perception_ptr, interaction_ptr, value_ptr, mixing_ptr, flow_ptr,
             None if m is None else _fp(m), None if s is None else _fp(s)))
+
+    def get_weights(self, set_index=0):
+        """(Wp, Wi, Wv, Wo, K, mu, sigma) of one set as held on the device (fp32 master copy)."""
+        out = [np.empty((8, 64, 64), np.float32) for _ in range(3)] + [np.empty((512, 64), np.float32),
+               np.empty((8, 9), np.float32), np.empty(8, np.float32), np.empty(8, np.float32)]
+        self._ck(lib().slime_ca_get_weights(self._h, set_index, *[_fp(a) for a in out]))
+        return tuple(out)
+
+    def evolve(self, *, fitness_threshold, hunger_threshold, mutation_rate, mutation_sigma, seed, generation, stream=0):
+        """The population step after fitness(): returns dict(parent=[n_sets], best=int, n_replaced=int)."""
+        p = EvolveParams(fitness_threshold, hunger_threshold, mutation_rate, mutation_sigma, seed, generation)
+        parent = np.empty(self.cfg.n_weight_sets, np.int32)
+        best, n = ctypes.c_int(-1), ctypes.c_int(0)
+        self._ck(lib().slime_ca_evolve(self._h, ctypes.byref(p), parent.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
+                                       ctypes.byref(best), ctypes.byref(n), stream))
+        return {"parent": parent, "best": best.value, "n_replaced": n.value}
 
     def pool_readout(self, Wr, br=None, stream=0):
         Wr = _f32(Wr)

@@ -15,6 +15,7 @@
 #include "ca_f32.cuh"
 #include "common.cuh"
 #include "fitness.cuh"
+#include "evolve.cuh"
 
 using namespace slime;
 
@@ -41,8 +42,13 @@ struct slime_ca {
     float* prm = nullptr;           // [sets][8][PRM]
     __nv_bfloat16* w1_bf16 = nullptr;  // [sets][8][192][64]  rows = output column (Wp|Wi|Wv), K = c_in contiguous
     __nv_bfloat16* wo_bf16 = nullptr;  // [sets][8][64][64]   rows = c_out, K = d contiguous
+    float* master = nullptr;        // [sets][MW_STRIDE] fp32 master copy in the upload's own index order
+    float* set_stats = nullptr;     // [sets][2] mean fitness, mean hunger of the last population step
+    int* parent = nullptr;          // [sets] parent of each set after the last population step
+    int* evolve_info = nullptr;     // {best set, replaced sets}
     std::vector<char> weights_set;
     bool state_set = false;
+    bool fitness_valid = false;     // fit_dev holds the fitness of the current V' pair
     // fitness scratch
     double* gram_part = nullptr;
     int gram_splits = 0;
@@ -249,6 +255,11 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
     CK(h, cudaMemset(h->dev_status, 0, sizeof(int)));
     const size_t sets = cfg->n_weight_sets;
     if ((rc = dev_alloc(h, &h->prm, sets * NH * PRM))) return rc;
+    if ((rc = dev_alloc(h, &h->master, sets * MW_STRIDE))) return rc;
+    CK(h, cudaMemset(h->master, 0, sets * MW_STRIDE * sizeof(float)));
+    if ((rc = dev_alloc(h, &h->set_stats, sets * 2))) return rc;
+    if ((rc = dev_alloc(h, &h->parent, sets))) return rc;
+    if ((rc = dev_alloc(h, &h->evolve_info, 2))) return rc;
     if (is_bf16(h)) {
         if ((rc = dev_alloc(h, &h->w1_bf16, sets * NH * 192 * 64))) return rc;
         if ((rc = dev_alloc(h, &h->wo_bf16, sets * NH * 64 * 64))) return rc;
@@ -269,7 +280,7 @@ int slime_ca_destroy(slime_ca* h) {
     cudaSetDevice(h->cfg.device);
     void* ptrs[] = {h->X, h->E, h->V, h->vprime[0], h->vprime[1], h->scale, h->mass, h->sums, h->partial, h->seg_sums,
                     h->wpiv_f32, h->wo_f32, h->prm, h->w1_bf16, h->wo_bf16, h->gram_part, h->head_rank,
-                    h->pearson_part, h->fit_dev, h->dev_status};
+                    h->pearson_part, h->fit_dev, h->dev_status, h->master, h->set_stats, h->parent, h->evolve_info};
     for (void* p : ptrs)
         if (p) cudaFree(p);
     delete h;
@@ -288,50 +299,20 @@ int slime_ca_set_weights(slime_ca* h, int set_index, const float* Wp, const floa
     for (int i = 0; i < NH; ++i)
         if (!(sigma[i] > 0.f)) return fail(h, SLIME_CA_EINVAL, "sigma must be positive");
     CK(h, cudaSetDevice(h->cfg.device));
-    std::vector<float> prm((size_t)NH * PRM, 0.f);
-    for (int hd = 0; hd < NH; ++hd) {
-        for (int t = 0; t < 9; ++t) prm[hd * PRM + t] = K[hd * 9 + t];
-        prm[hd * PRM + 9] = mu[hd];
-        prm[hd * PRM + 10] = -1.f / (2.f * sigma[hd] * sigma[hd]);
-    }
-    if (is_bf16(h)) {
-        // The bf16 kernels evaluate the growth bell and the softmax numerator in base 2 with the constants folded
-        // into the weights: Wp is scaled by s = sqrt(log2(e) / (2 sigma^2)) and Wi by log2(e), so that
-        // G = 2 exp2(-(U' - mu s)^2) - 1 and E = exp2(G I').  Slot 9 of the parameter block carries mu * s.
-        for (int hd = 0; hd < NH; ++hd) {
-            const float s = sqrtf(1.4426950408889634f / (2.f * sigma[hd] * sigma[hd]));
-            prm[hd * PRM + 9] = mu[hd] * s;
-            prm[hd * PRM + 10] = s;
-        }
-    }
-    CK(h, cudaMemcpy(h->prm + (size_t)set_index * NH * PRM, prm.data(), prm.size() * sizeof(float), cudaMemcpyHostToDevice));
-    if (is_bf16(h)) {
-        // B operands are stored "K-major": one row per output column, the 64 inputs contiguous.
-        std::vector<__nv_bfloat16> w1((size_t)NH * 192 * 64), wo((size_t)NH * 64 * 64);
-        for (int hd = 0; hd < NH; ++hd)
-            for (int c = 0; c < NC; ++c)
-                for (int d = 0; d < HD; ++d) {
-                    const size_t src = ((size_t)hd * NC + c) * HD + d;
-                    w1[((size_t)hd * 192 + d) * 64 + c] = __float2bfloat16(Wp[src] * prm[hd * PRM + 10]);
-                    w1[((size_t)hd * 192 + 64 + d) * 64 + c] = __float2bfloat16(Wi[src] * 1.4426950408889634f);
-                    w1[((size_t)hd * 192 + 128 + d) * 64 + c] = __float2bfloat16(Wv[src]);
-                    // Wo[(hd*64+d)][c] -> row c (output channel), column d
-                    wo[((size_t)hd * 64 + c) * 64 + d] = __float2bfloat16(Wo[((size_t)hd * HD + d) * NC + c]);
-                }
-        CK(h, cudaMemcpy(h->w1_bf16 + (size_t)set_index * NH * 192 * 64, w1.data(), w1.size() * 2, cudaMemcpyHostToDevice));
-        CK(h, cudaMemcpy(h->wo_bf16 + (size_t)set_index * NH * 64 * 64, wo.data(), wo.size() * 2, cudaMemcpyHostToDevice));
-    } else {
-        std::vector<float> w((size_t)NH * NC * 192);
-        for (int hd = 0; hd < NH; ++hd)
-            for (int c = 0; c < NC; ++c)
-                for (int d = 0; d < HD; ++d) {
-                    const size_t src = ((size_t)hd * NC + c) * HD + d;
-                    const size_t dst = ((size_t)hd * NC + c) * 192 + d;
-                    w[dst] = Wp[src]; w[dst + 64] = Wi[src]; w[dst + 128] = Wv[src];
-                }
-        CK(h, cudaMemcpy(h->wpiv_f32 + (size_t)set_index * NH * NC * 192, w.data(), w.size() * sizeof(float), cudaMemcpyHostToDevice));
-        CK(h, cudaMemcpy(h->wo_f32 + (size_t)set_index * NH * HD * NC, Wo, (size_t)NH * HD * NC * sizeof(float), cudaMemcpyHostToDevice));
-    }
+    // The fp32 master copy stays on the device (the population step mutates it there); the operand layouts of
+    // the step kernels are derived from it by a kernel.
+    float* m = h->master + (size_t)set_index * MW_STRIDE;
+    CK(h, cudaMemcpy(m + MW_WP, Wp, (size_t)NH * NC * HD * sizeof(float), cudaMemcpyHostToDevice));
+    CK(h, cudaMemcpy(m + MW_WI, Wi, (size_t)NH * NC * HD * sizeof(float), cudaMemcpyHostToDevice));
+    CK(h, cudaMemcpy(m + MW_WV, Wv, (size_t)NH * NC * HD * sizeof(float), cudaMemcpyHostToDevice));
+    CK(h, cudaMemcpy(m + MW_WO, Wo, (size_t)NH * HD * NC * sizeof(float), cudaMemcpyHostToDevice));
+    CK(h, cudaMemcpy(m + MW_K, K, NH * 9 * sizeof(float), cudaMemcpyHostToDevice));
+    CK(h, cudaMemcpy(m + MW_MU, mu, NH * sizeof(float), cudaMemcpyHostToDevice));
+    CK(h, cudaMemcpy(m + MW_SIGMA, sigma, NH * sizeof(float), cudaMemcpyHostToDevice));
+    k_weights_layout<<<dim3(32, 1), 256>>>(h->master, nullptr, set_index, is_bf16(h) ? 1 : 0, h->wpiv_f32, h->wo_f32,
+                                           h->w1_bf16, h->wo_bf16, h->prm);
+    LAUNCHED(h);
+    CK(h, cudaStreamSynchronize(nullptr));
     h->weights_set[set_index] = 1;
     return SLIME_CA_OK;
 }
@@ -355,7 +336,7 @@ int slime_ca_set_state_device(slime_ca* h, const void* dev_state, int dtype, voi
     int rc = channel_sums(h, 1, st);
     if (rc) return rc;
     h->state_set = true;
-    h->vp_steps = 0;
+    h->vp_steps = 0; h->fitness_valid = false;
     return SLIME_CA_OK;
 }
 
@@ -425,7 +406,7 @@ int slime_ca_step_partial(slime_ca* h, void* stream) {
     if (rc) return rc;
     CK(h, cudaSetDevice(h->cfg.device));
     void* emit = nullptr;
-    if (h->cfg.keep_vprime) { h->vp_last ^= 1; emit = h->vprime[h->vp_last]; ++h->vp_steps; }
+    if (h->cfg.keep_vprime) { h->vp_last ^= 1; emit = h->vprime[h->vp_last]; ++h->vp_steps; h->fitness_valid = false; }
     rc = step_kernels(h, emit, (cudaStream_t)stream);
     if (rc) return rc;
     ++h->steps_done;
@@ -451,7 +432,7 @@ int slime_ca_step(slime_ca* h, int n_steps, void* stream) {
     const int n = h->g.B * NC;
     for (int i = 0; i < n_steps; ++i) {
         void* emit = nullptr;
-        if (h->cfg.keep_vprime && i >= n_steps - 2) { h->vp_last ^= 1; emit = h->vprime[h->vp_last]; ++h->vp_steps; }
+        if (h->cfg.keep_vprime && i >= n_steps - 2) { h->vp_last ^= 1; emit = h->vprime[h->vp_last]; ++h->vp_steps; h->fitness_valid = false; }
         rc = step_kernels(h, emit, st);
         if (rc) return rc;
         k_scale_from_sums<<<(n + 255) / 256, 256, 0, st>>>(h->sums, h->mass, h->scale, n);
@@ -543,7 +524,55 @@ int slime_ca_fitness(slime_ca* h, float* rank, float* coherence, float* fitness,
         if (fitness) fitness[b] = out[b * 4 + 2];
         if (hunger) hunger[b] = out[b * 4 + 3];
     }
+    h->fitness_valid = true;
     return check_status_word(h);
+}
+
+int slime_ca_get_weights(slime_ca* h, int set_index, float* Wp, float* Wi, float* Wv, float* Wo, float* K, float* mu,
+                         float* sigma) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (set_index < 0 || set_index >= h->cfg.n_weight_sets) return fail(h, SLIME_CA_EINVAL, "weight set index out of range");
+    if (!h->weights_set[set_index]) return fail(h, SLIME_CA_ESTATE, "this weight set has not been uploaded");
+    CK(h, cudaSetDevice(h->cfg.device));
+    const float* m = h->master + (size_t)set_index * MW_STRIDE;
+    const size_t nm = (size_t)NH * NC * HD * sizeof(float);
+    if (Wp) CK(h, cudaMemcpy(Wp, m + MW_WP, nm, cudaMemcpyDeviceToHost));
+    if (Wi) CK(h, cudaMemcpy(Wi, m + MW_WI, nm, cudaMemcpyDeviceToHost));
+    if (Wv) CK(h, cudaMemcpy(Wv, m + MW_WV, nm, cudaMemcpyDeviceToHost));
+    if (Wo) CK(h, cudaMemcpy(Wo, m + MW_WO, nm, cudaMemcpyDeviceToHost));
+    if (K) CK(h, cudaMemcpy(K, m + MW_K, NH * 9 * sizeof(float), cudaMemcpyDeviceToHost));
+    if (mu) CK(h, cudaMemcpy(mu, m + MW_MU, NH * sizeof(float), cudaMemcpyDeviceToHost));
+    if (sigma) CK(h, cudaMemcpy(sigma, m + MW_SIGMA, NH * sizeof(float), cudaMemcpyDeviceToHost));
+    return SLIME_CA_OK;
+}
+
+int slime_ca_evolve(slime_ca* h, const slime_ca_evolve_params* p, int* parent, int* best_set, int* n_replaced,
+                    void* stream) {
+    int rc = ready(h);
+    if (rc) return rc;
+    if (!p) return fail(h, SLIME_CA_EINVAL, "null parameters");
+    if (!(p->mutation_rate >= 0.f && p->mutation_rate <= 1.f) || !(p->mutation_sigma >= 0.f))
+        return fail(h, SLIME_CA_EINVAL, "mutation_rate must lie in [0, 1] and mutation_sigma must not be negative");
+    if (!h->cfg.keep_vprime || !h->fitness_valid)
+        return fail(h, SLIME_CA_ESTATE, "the population step follows slime_ca_fitness on the same state");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const int sets = h->cfg.n_weight_sets;
+    EvolveParams ep{p->fitness_threshold, p->hunger_threshold, p->mutation_rate, p->mutation_sigma, p->seed, p->generation};
+    k_evolve_select<<<1, 256, 0, st>>>(h->fit_dev, sets, h->g.per_set, ep, h->set_stats, h->parent, h->evolve_info);
+    LAUNCHED(h);
+    k_evolve_refill<<<dim3(32, sets), 256, 0, st>>>(h->master, h->parent, ep);
+    LAUNCHED(h);
+    k_weights_layout<<<dim3(32, sets), 256, 0, st>>>(h->master, h->parent, 0, is_bf16(h) ? 1 : 0, h->wpiv_f32, h->wo_f32,
+                                                     h->w1_bf16, h->wo_bf16, h->prm);
+    LAUNCHED(h);
+    int info[2] = {-1, 0};
+    CK(h, cudaMemcpyAsync(info, h->evolve_info, sizeof(info), cudaMemcpyDeviceToHost, st));
+    if (parent) CK(h, cudaMemcpyAsync(parent, h->parent, sets * sizeof(int), cudaMemcpyDeviceToHost, st));
+    CK(h, cudaStreamSynchronize(st));
+    if (best_set) *best_set = info[0];
+    if (n_replaced) *n_replaced = info[1];
+    return SLIME_CA_OK;
 }
 
 int slime_ca_lift_images(slime_ca* h, const float* host_img, int img_h, int img_w, const float* host_L, void* stream) {
@@ -566,7 +595,7 @@ int slime_ca_lift_images(slime_ca* h, const float* host_img, int img_h, int img_
     if (rc) return rc;
     CK(h, cudaStreamSynchronize(st));
     h->state_set = true;
-    h->vp_steps = 0;
+    h->vp_steps = 0; h->fitness_valid = false;
     return SLIME_CA_OK;
 }
 
@@ -607,7 +636,7 @@ int slime_ca_lift_field_device(slime_ca* h, const float* dev_field, const float*
     if (rc) return rc;
     CK(h, cudaStreamSynchronize(st));
     h->state_set = true;
-    h->vp_steps = 0;
+    h->vp_steps = 0; h->fitness_valid = false;
     return SLIME_CA_OK;
 }
 
