@@ -13,13 +13,21 @@ constexpr int GRAM_CHUNK = 2048;   // cells per Gram partial
 constexpr int JSTRIDE = 65;        // padded row stride of the Jacobi matrix in shared memory (doubles)
 
 // gram_part[((b*8+h)*splits + split)][64][64] (fp64) over cells [split*GRAM_CHUNK, ...) of plane (b,h).
+// The Gram matrix is symmetric: only the 136 4x4 blocks on or above the diagonal are accumulated (one thread
+// each, 160 threads per block) and each is written to both places.
+constexpr int GRAM_THREADS = 160;
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(GRAM_THREADS)
 k_gram(const T* __restrict__ vp, int cells, double* __restrict__ gram_part) {
     __shared__ __align__(16) float f[64][68];
     const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
     const T* plane = vp + ((size_t)b * NH + h) * (size_t)cells * HD;
-    const int ti = (threadIdx.x >> 4) * 4, tj = (threadIdx.x & 15) * 4;
+    // thread t -> block (bi, bj), bi <= bj, rows of the upper triangle laid end to end: row bi starts at
+    // bi * 16 - bi * (bi - 1) / 2
+    int bi = 0, rest = threadIdx.x;
+    const bool live = threadIdx.x < 136;
+    if (live) { while (rest >= 16 - bi) { rest -= 16 - bi; ++bi; } } else rest = 0;
+    const int ti = bi * 4, tj = (bi + rest) * 4;
     double acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -29,65 +37,79 @@ k_gram(const T* __restrict__ vp, int cells, double* __restrict__ gram_part) {
     const int hi = min(lo + GRAM_CHUNK, cells);
     for (int s0 = lo; s0 < hi; s0 += 64) {
         __syncthreads();
-        for (int i = threadIdx.x; i < 64 * 64; i += 256) {
+        for (int i = threadIdx.x; i < 64 * 64; i += GRAM_THREADS) {
             const int s = s0 + (i >> 6);
             f[i >> 6][i & 63] = s < hi ? to_f32<T>(plane[(size_t)s * HD + (i & 63)]) : 0.f;
         }
         __syncthreads();
+        if (live) {
 #pragma unroll 4
-        for (int s = 0; s < 64; ++s) {
-            const float4 a = *reinterpret_cast<const float4*>(&f[s][ti]);
-            const float4 c = *reinterpret_cast<const float4*>(&f[s][tj]);
-            const double av[4] = {a.x, a.y, a.z, a.w};
-            const double cv[4] = {c.x, c.y, c.z, c.w};
+            for (int s = 0; s < 64; ++s) {
+                const float4 a = *reinterpret_cast<const float4*>(&f[s][ti]);
+                const float4 c = *reinterpret_cast<const float4*>(&f[s][tj]);
+                const double av[4] = {a.x, a.y, a.z, a.w};
+                const double cv[4] = {c.x, c.y, c.z, c.w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+                for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fma(av[i], cv[j], acc[i][j]);
+                    for (int j = 0; j < 4; ++j) acc[i][j] = fma(av[i], cv[j], acc[i][j]);
+            }
         }
     }
+    if (!live) return;
     double* out = gram_part + (((size_t)b * NH + h) * splits + split) * (HD * HD);
 #pragma unroll
     for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j) out[(ti + i) * HD + tj + j] = acc[i][j];
+        for (int j = 0; j < 4; ++j) {
+            out[(ti + i) * HD + tj + j] = acc[i][j];
+            if (ti != tj) out[(tj + j) * HD + ti + i] = acc[i][j];
+        }
 }
 
-// One warp per (grid, head): sum the Gram partials, diagonalise by two-sided Jacobi with a round-robin
-// (tournament) ordering - 32 disjoint rotations per round, 63 rounds per sweep - until the off-diagonal
-// Frobenius norm is <= 1e-6 x the matrix norm, plus one more sweep, at most 30 sweeps
+// One 128-thread block per (grid, head): sum the Gram partials, diagonalise by two-sided Jacobi with a
+// round-robin (tournament) ordering - 32 disjoint rotations per round, 63 rounds per sweep - until the
+// off-diagonal Frobenius norm is <= 1e-6 x the matrix norm, plus one more sweep, at most 30 sweeps
 // (rotation formula of slime/kernels/warp_ca.cu:51-63, sweep limit :20), then the exp-entropy rank
 // p = l/(sum l + 1e-7), rank = exp(-sum p ln(p + 1e-7))  (slime/kernels/warp_ca.cu:107-144).
-__global__ void __launch_bounds__(32)
+// Thread t works on rotation pair t % 32 and on a quarter (t / 32) of the 64 elements of its two columns / rows.
+constexpr int JACOBI_THREADS = 128;
+__device__ __forceinline__ double jacobi_block_sum(double v, double* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    return (red[0] + red[1]) + (red[2] + red[3]);
+}
+__global__ void __launch_bounds__(JACOBI_THREADS)
 k_jacobi_rank(const double* __restrict__ gram_part, int splits, float* __restrict__ head_rank) {
     __shared__ double A[64 * JSTRIDE];
-    const int m = blockIdx.x, lane = threadIdx.x;
+    __shared__ double red[4];
+    const int m = blockIdx.x, tid = threadIdx.x, pair = tid & 31, k0 = (tid >> 5) * 16;
     const double* src = gram_part + (size_t)m * splits * (HD * HD);
     double fro2 = 0.0;
-    for (int i = lane; i < HD * HD; i += 32) {
+    for (int i = tid; i < HD * HD; i += JACOBI_THREADS) {
         double s = 0.0;
         for (int k = 0; k < splits; ++k) s += src[(size_t)k * (HD * HD) + i];
         A[(i >> 6) * JSTRIDE + (i & 63)] = s;
         fro2 += s * s;
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) fro2 += __shfl_xor_sync(0xffffffffu, fro2, o);
-    __syncwarp();
+    fro2 = jacobi_block_sum(fro2, red);
 
     int extra = 0;
     for (int sweep = 0; sweep < 30; ++sweep) {
         double off2 = 0.0;
-        for (int i = lane; i < HD * HD; i += 32) {
+        for (int i = tid; i < HD * HD; i += JACOBI_THREADS) {
             const int r = i >> 6, c = i & 63;
             if (r != c) { const double v = A[r * JSTRIDE + c]; off2 += v * v; }
         }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) off2 += __shfl_xor_sync(0xffffffffu, off2, o);
+        off2 = jacobi_block_sum(off2, red);          // the same value in every thread: the exit below is uniform
         if (off2 <= 1e-12 * fro2) { if (extra) break; extra = 1; }
         for (int round = 0; round < 63; ++round) {
             int p, q;
-            if (lane == 0) { p = 63; q = round; }
-            else { p = (round + lane) % 63; q = (round + 63 - lane) % 63; }
+            if (pair == 0) { p = 63; q = round; }
+            else { p = (round + pair) % 63; q = (round + 63 - pair) % 63; }
             if (p > q) { const int t = p; p = q; q = t; }
             const double apq = A[p * JSTRIDE + q];
             double c = 1.0, s = 0.0;
@@ -97,21 +119,23 @@ k_jacobi_rank(const double* __restrict__ gram_part, int splits, float* __restric
                 c = 1.0 / sqrt(1.0 + t * t);
                 s = t * c;
             }
-            __syncwarp();
-            for (int k = 0; k < 64; ++k) {          // columns p, q
+            __syncthreads();
+            for (int k = k0; k < k0 + 16; ++k) {    // columns p, q
                 const double akp = A[k * JSTRIDE + p], akq = A[k * JSTRIDE + q];
                 A[k * JSTRIDE + p] = c * akp - s * akq;
                 A[k * JSTRIDE + q] = s * akp + c * akq;
             }
-            __syncwarp();
-            for (int k = 0; k < 64; ++k) {          // rows p, q
+            __syncthreads();
+            for (int k = k0; k < k0 + 16; ++k) {    // rows p, q
                 const double apk = A[p * JSTRIDE + k], aqk = A[q * JSTRIDE + k];
                 A[p * JSTRIDE + k] = c * apk - s * aqk;
                 A[q * JSTRIDE + k] = s * apk + c * aqk;
             }
-            __syncwarp();
+            __syncthreads();
         }
     }
+    if (tid >= 32) return;
+    const int lane = tid;
     double l0 = fmax(A[lane * JSTRIDE + lane], 0.0), l1 = fmax(A[(lane + 32) * JSTRIDE + lane + 32], 0.0);
     double sum = l0 + l1;
 #pragma unroll

@@ -501,17 +501,17 @@ int slime_ca_fitness(slime_ca* h, float* rank, float* coherence, float* fitness,
     const void* vb = h->vprime[h->vp_last];
     const size_t per_grid = (size_t)cells * HC;
     if (is_bf16(h)) {
-        k_gram<__nv_bfloat16><<<dim3(h->gram_splits, NH, g.B), 256, 0, st>>>((const __nv_bfloat16*)vb, cells, h->gram_part);
+        k_gram<__nv_bfloat16><<<dim3(h->gram_splits, NH, g.B), GRAM_THREADS, 0, st>>>((const __nv_bfloat16*)vb, cells, h->gram_part);
         LAUNCHED(h);
         k_pearson<__nv_bfloat16><<<dim3(h->pearson_splits, g.B), 256, 0, st>>>((const __nv_bfloat16*)va, (const __nv_bfloat16*)vb, per_grid, h->pearson_part);
         LAUNCHED(h);
     } else {
-        k_gram<float><<<dim3(h->gram_splits, NH, g.B), 256, 0, st>>>((const float*)vb, cells, h->gram_part);
+        k_gram<float><<<dim3(h->gram_splits, NH, g.B), GRAM_THREADS, 0, st>>>((const float*)vb, cells, h->gram_part);
         LAUNCHED(h);
         k_pearson<float><<<dim3(h->pearson_splits, g.B), 256, 0, st>>>((const float*)va, (const float*)vb, per_grid, h->pearson_part);
         LAUNCHED(h);
     }
-    k_jacobi_rank<<<g.B * NH, 32, 0, st>>>(h->gram_part, h->gram_splits, h->head_rank);
+    k_jacobi_rank<<<g.B * NH, JACOBI_THREADS, 0, st>>>(h->gram_part, h->gram_splits, h->head_rank);
     LAUNCHED(h);
     k_fitness_final<<<(g.B + 127) / 128, 128, 0, st>>>(h->head_rank, h->pearson_part, h->pearson_splits, (double)per_grid, h->fit_dev, g.B);
     LAUNCHED(h);

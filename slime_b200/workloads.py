@@ -4,7 +4,8 @@
   python -m torch.distributed.run --nproc-per-node N -m slime_b200.workloads --config 3|4|5
 
   1  the CPU-runnable reference model: X[1,128,128,64] fp32, 16 steps
-  3  batch-sharded population: 1024 grids, 128 weight sets x 8 grids, 32 steps, then fitness per grid
+  3  batch-sharded population: 1024 grids, 128 weight sets x 8 grids, 32 steps, then fitness per grid and the
+     population step (cull below the median, refill from the best) on each rank's share
   4  one large torus split into row stripes: X[1,8192,8192,64] bf16, 100 steps, halo exchange + mass all-reduce
   5  supervised-input shape: 4096 images 28x28 -> 32x32x64, 24 steps, mean-pool + 64->10 read-out
 
@@ -84,6 +85,15 @@ def config3(args, rank, world, local):
     ms = _timed(lambda: h.step(steps), world)
     ms_fit = _timed(lambda: h.fitness(), world)
     fit = h.fitness()
+    # the population step that consumes the fitness: cull the sets below the median, refill them from the best
+    set_fit = fit["fitness"].astype(np.float64).reshape(sh.n_sets, -1).mean(1)
+    thr = float(10.0 * np.nanmedian(set_fit))
+    evo = {}
+
+    def population_step():
+        evo.update(h.evolve(fitness_threshold=thr, hunger_threshold=2.0, mutation_rate=0.01, mutation_sigma=0.0125,
+                            seed=42, generation=1))
+    ms_evolve = _timed(population_step, world)
     h.close()
     local_stats = torch.tensor([float(np.nanmean(fit["rank"])), float(np.nanmean(fit["coherence"])),
                                 float(np.isfinite(fit["fitness"]).mean())], device="cuda", dtype=torch.float64)
@@ -91,7 +101,8 @@ def config3(args, rank, world, local):
         dist.all_reduce(local_stats, op=dist.ReduceOp.SUM)
         local_stats /= world
     return {"config": 3, "workload": f"{n_grids} grids 128x128x64, {n_sets} weight sets, {steps} steps + fitness",
-            "dtype": args.dtype, "n_gpus": world, "ms": ms, "ms_fitness": ms_fit,
+            "dtype": args.dtype, "n_gpus": world, "ms": ms, "ms_fitness": ms_fit, "ms_population_step": ms_evolve,
+            "sets_replaced_rank0": int(evo["n_replaced"]),
             "cell_updates_per_s": n_grids * 128 * 128 * steps / (ms * 1e-3),
             "mean_rank": float(local_stats[0]), "mean_coherence": float(local_stats[1]),
             "finite_fraction": float(local_stats[2]), "scaling": "strong (1024 grids split over the ranks)"}
