@@ -169,3 +169,25 @@ def test_batch_of_64_invariants(gpu):
     m0, m1 = channel_mass(bf16_round(X0)), channel_mass(X1)
     assert np.max(np.abs(m1 - m0) / np.abs(m0)) < TOL_MASS
     h.close()
+
+
+def test_torus_shift_equivariance_full_size(gpu):
+    """A size-independent property at the training shape: rolling every grid on its torus rolls the step's output.
+    The stored (un-normalised) state and V' are compared bit for bit - each cell's arithmetic does not depend on
+    where the cell sits in a tile - so a wrong apron copy, halo or tile edge anywhere on the 128 x 128 grids shows."""
+    import torch
+    capi, devmem = gpu
+    B, H, W = 16, 128, 128
+    X0 = bf16_round(inputs.make_state(B, H, W, seed=13, scale=0.45 * H * W))
+    w = inputs.make_weight_sets(2, seed=13)
+    dy, dx = 5, -19
+    outs = []
+    for X in (X0, np.roll(X0, (dy, dx), axis=(1, 2))):
+        with capi.Handle(B, H, W, n_weight_sets=2, dtype=capi.BF16, keep_vprime=True) as h:
+            h.set_weights(w)
+            h.set_state(X)
+            h.step(1)
+            torch.cuda.synchronize()
+            outs.append((devmem.state_view(h).float().cpu().numpy().reshape(B, H, W, 64), devmem.vprime(h, capi.BUF_VPRIME_LAST)))
+    assert np.array_equal(np.roll(outs[0][1], (dy, dx), axis=(1, 2)), outs[1][1])
+    assert np.array_equal(np.roll(outs[0][0], (dy, dx), axis=(1, 2)), outs[1][0])
