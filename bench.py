@@ -91,11 +91,12 @@ def cpu_baseline(ca_steps_sample=2, grids=1):
     from slime_b200 import inputs
     X = inputs.make_state(grids, GRID, GRID, seed=42)
     w = inputs.make_weight_sets(1, seed=42)
+    # all the host threads this process may use, whatever OMP_NUM_THREADS the launcher exported
+    cores = ca_oracle.set_threads(ca_oracle.usable_cpus(), real="f32")
     ca_oracle.ca_steps(X[:1, :16, :16].copy(), w, 1, literal=False, real="f32")       # load + warm the library
     t0 = time.perf_counter()
     ca_oracle.ca_steps(X, w, ca_steps_sample, literal=False, real="f32")
     dt = time.perf_counter() - t0
-    cores = len(os.sched_getaffinity(0))
     return {"value": grids * GRID * GRID * ca_steps_sample / dt, "unit": UNIT, "cores": cores, "kind": "port", "seconds": dt,
             "sample": f"{grids} grid(s) of {GRID}x{GRID}x64, {ca_steps_sample} CA steps, fp32, OpenMP on {cores} threads "
                       f"({dt:.1f} s)"}

@@ -34,6 +34,9 @@
  *   failed_attempts/pseudopod.cu:366-432, slime/kernels/warp_ca.cu:51-63,107-144,219,238.
  */
 #include <math.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
 #include <stdint.h>
 #include <stdlib.h>
 #include <string.h>
@@ -564,5 +567,17 @@ int oracle_evolve(const float* fit, int n_sets, int per_set, float fitness_thres
             }
     }
     return replaced;
+}
+
+/* Threads the OpenMP loops above use from now on (n <= 0: leave as is); returns the count in force.  Launchers
+ * that start one process per GPU export OMP_NUM_THREADS=1, which is not what a timed CPU baseline wants. */
+int oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
 }
 

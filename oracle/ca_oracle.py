@@ -53,6 +53,8 @@ def _lib(real: str):
         lib.oracle_field_from_state.argtypes = [_F, ctypes.c_int, ctypes.c_int, _F]
         lib.oracle_weights_from_reference_layout.restype = None
         lib.oracle_weights_from_reference_layout.argtypes = [_F] * 10
+        lib.oracle_set_threads.restype = ctypes.c_int
+        lib.oracle_set_threads.argtypes = [ctypes.c_int]
         lib.oracle_evolve.restype = ctypes.c_int
         lib.oracle_evolve.argtypes = [_F, ctypes.c_int, ctypes.c_int, ctypes.c_float, ctypes.c_float, ctypes.c_float,
                                       ctypes.c_float, ctypes.c_ulonglong, ctypes.c_int, _F, _F, _F, _F,
@@ -184,3 +186,22 @@ def evolve(fit, weights, per_set, *, fitness_threshold, hunger_threshold, mutati
                                   parent.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), ctypes.byref(best))
     K, mu, sigma = K[parent], mu[parent], sigma[parent]      # taps, mu and sigma are inherited unchanged
     return (Wp, Wi, Wv, Wo, K, mu, sigma), parent, best.value, n
+
+
+def usable_cpus():
+    """CPUs this process may really use: the affinity mask, capped by the cgroup CPU quota when there is one."""
+    import math
+    import os
+    n = len(os.sched_getaffinity(0))
+    try:
+        quota, period = open("/sys/fs/cgroup/cpu.max").read().split()
+        if quota != "max":
+            n = max(1, min(n, math.ceil(int(quota) / int(period))))
+    except (OSError, ValueError):
+        pass
+    return n
+
+
+def set_threads(n, real="f32"):
+    """Set the OpenMP thread count of one build of the oracle; returns the count in force."""
+    return int(_lib(real).oracle_set_threads(int(n)))
