@@ -161,7 +161,9 @@ def config5(args, rank, world, local):
         logits = h.pool_readout(Wr, br)
     return {"config": 5, "workload": f"{n_img} images 28x28 -> 32x32x64, {steps} steps, mean-pool + 64->10 read-out",
             "dtype": args.dtype, "n_gpus": world, "ms": ms, "cell_updates_per_s": n_img * 32 * 32 * steps / (ms * 1e-3),
-            "logits_finite": bool(np.isfinite(logits).all()), "logit0": [float(v) for v in logits[0][:3]]}
+            "logits_finite": bool(np.isfinite(logits).all()), "logit0": [float(v) for v in logits[0][:3]],
+            "note": "the lifted states (mass ~100 per channel) diverge under random weights: the fp64 CPU oracle of "
+                    "this workload is itself non-finite by step 16; throughput does not depend on the values"}
 
 
 def main():
