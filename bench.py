@@ -246,7 +246,7 @@ def main():
                            "parallelism": f"batch-sharded x{world}, no data-path collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
                 "state_finite_after_steps": finite_after}
-        if not args.no_cpu_baseline:
+        if not args.no_cpu_baseline and world == 1:       # the CPU baseline is timed at N = 1 only
             line["cpu_baseline"] = cpu_baseline(ca_steps_sample=CA_STEPS, grids=8)   # 8 of the 64 grids: 10-15 s
         print(json.dumps(line), flush=True)
     h.close()
