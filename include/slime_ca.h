@@ -210,6 +210,23 @@ int slime_ca_set_weights_reference_layout(slime_ca* h, int set_index, const floa
                                           const float* dev_head_mixing, const float* dev_flow_kernels,
                                           const float* mu, const float* sigma);
 
+/*
+ * One line of the reference's trajectory file evolution.json (extract_system_state, slime/extract_state.cu:58-184,
+ * written every 100 generations by slime/runtime.cu:402-408) for one grid, into `buf` (NUL-terminated, `cap`
+ * bytes; *written = length without the NUL, also when `cap` is too small, which returns SLIME_CA_EINVAL):
+ *   {"gen":G,"elapsed":S.SS,"chemical":{"concentration":[16 x 16 centre sample, %.4f],"size":16},
+ *    "ca":{"flow_kernels":[[9 x %.4f] x 8]},"agents":[],"voronoi":[],"archive":{"size":0,"elites":[]},
+ *    "pool":{"active":A,"capacity":C,"spawned":S,"culled":K}}\n
+ * with the reference's key order and number formats, so the two files can be read by the same tools.  The
+ * concentration is sampled from `dev_field` (DEVICE [height][width] fp32) or, when NULL, from the channel mean of
+ * the grid's normalised state; the flow kernels are those of the grid's weight set.  Agents, Voronoi cells and the
+ * elite archive belong to subsystems outside this library and are written empty; the pool counters are the
+ * caller's (e.g. from slime_ca_evolve).  Synchronises `stream`.
+ */
+int slime_ca_evolution_record(slime_ca* h, int grid_index, int generation, double elapsed_seconds,
+                              const float* dev_field, int pool_active, int pool_capacity, int pool_spawned,
+                              int pool_culled, char* buf, size_t cap, size_t* written, void* stream);
+
 /* Number of kernels the library has launched on this handle since creation (for launch accounting). */
 long long slime_ca_launch_count(const slime_ca* h);
 

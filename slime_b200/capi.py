@@ -26,7 +26,7 @@ SYMBOLS = (
     "slime_ca_lift_images", "slime_ca_pool_readout", "slime_ca_launch_count", "launch_multi_head_ca",
     "slime_ca_channel_sums_static", "slime_ca_static_error",
     "slime_ca_lift_field_device", "slime_ca_field_from_state_device", "slime_ca_set_weights_reference_layout",
-    "slime_ca_get_weights", "slime_ca_evolve",
+    "slime_ca_get_weights", "slime_ca_evolve", "slime_ca_evolution_record",
 )
 
 
@@ -86,6 +86,8 @@ def lib():
         L.slime_ca_get_weights.argtypes = [vp, ctypes.c_int] + [fp] * 7
         ip = ctypes.POINTER(ctypes.c_int)
         L.slime_ca_evolve.argtypes = [vp, ctypes.POINTER(EvolveParams), ip, ip, ip, vp]
+        L.slime_ca_evolution_record.argtypes = [vp, ctypes.c_int, ctypes.c_int, ctypes.c_double, vp] + [ctypes.c_int] * 4 + \
+                                               [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t), vp]
         L.slime_ca_launch_count.argtypes = [vp]
         L.slime_ca_launch_count.restype = ctypes.c_longlong
         L.launch_multi_head_ca.argtypes = [vp, vp, vp, ctypes.c_int, ctypes.c_int]
@@ -267,6 +269,15 @@ class Handle:
         self._ck(lib().slime_ca_evolve(self._h, ctypes.byref(p), parent.ctypes.data_as(ctypes.POINTER(ctypes.c_int)),
                                        ctypes.byref(best), ctypes.byref(n), stream))
         return {"parent": parent, "best": best.value, "n_replaced": n.value}
+
+    def evolution_record(self, grid_index, generation, elapsed, *, dev_field_ptr=None, active=0, capacity=0, spawned=0,
+                         culled=0, stream=0):
+        """One line of the reference's evolution.json for one grid (str, newline-terminated)."""
+        buf = ctypes.create_string_buffer(16384)
+        n = ctypes.c_size_t(0)
+        self._ck(lib().slime_ca_evolution_record(self._h, grid_index, generation, elapsed, dev_field_ptr, active, capacity,
+                                                 spawned, culled, buf, len(buf), ctypes.byref(n), stream))
+        return buf.value.decode()
 
     def pool_readout(self, Wr, br=None, stream=0):
         Wr = _f32(Wr)

@@ -57,29 +57,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     return false;
 }
 
-// Same contract, for the single-lane producer / issuer threads whose wake-up latency sits on the pipeline's
-// critical path: polls with the non-blocking test_wait instead of the suspending try_wait.
-__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, int* status, int code) {
-    uint64_t t0 = 0;
-    for (uint32_t i = 0; i < WAIT_LIMIT_POLLS; ++i) {
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((i & 1023u) == 1023u) {
-            if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-            const uint64_t t = globaltimer_ns();
-            if (t0 == 0) t0 = t;
-            else if (t - t0 > WAIT_LIMIT_NS) break;
-        }
-    }
-    atomicCAS(status, 0, code);
-    return false;
-}
-
 // ---- proxies and fences ----------------------------------------------------------------------------------
 // makes this thread's shared-memory writes visible to the async proxy (UMMA operand reads, TMA)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -120,13 +97,6 @@ __device__ __forceinline__ void bar_sync(int id, int count) {
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");
 }
-
-// ---- cp.async (16-byte, L2 only) -------------------------------------------------------------------------
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ---- TMEM ---------------------------------------------------------------------------------------------------
 // One full warp allocates `cols` (power of two >= 32) TMEM columns; the base address lands in *smem_out.

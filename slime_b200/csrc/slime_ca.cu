@@ -691,6 +691,58 @@ int slime_ca_set_weights_reference_layout(slime_ca* h, int set_index, const floa
                                 mu ? mu : mu_d.data(), sigma ? sigma : sg_d.data());
 }
 
+int slime_ca_evolution_record(slime_ca* h, int grid_index, int generation, double elapsed_seconds,
+                              const float* dev_field, int pool_active, int pool_capacity, int pool_spawned,
+                              int pool_culled, char* buf, size_t cap, size_t* written, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!buf || cap == 0 || grid_index < 0 || grid_index >= h->g.B) return fail(h, SLIME_CA_EINVAL, "bad record arguments");
+    if (!h->state_set && !dev_field) return fail(h, SLIME_CA_ESTATE, "no state has been loaded");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const Geom& g = h->g;
+    const int set = grid_index / g.per_set;
+    if (!h->weights_set[set]) return fail(h, SLIME_CA_ESTATE, "this grid's weight set has not been uploaded");
+    // the field: the caller's, or the channel mean of the CA state (scratch: the E buffer, free between steps)
+    const float* field = dev_field;
+    if (!field) {
+        float* scratch = (float*)h->E;
+        const int blocks = grid_for((size_t)g.B * g.H * g.W * 8);
+        if (is_bf16(h)) k_channel_mean<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)h->X, h->scale, scratch, g);
+        else k_channel_mean<float><<<blocks, 256, 0, st>>>((const float*)h->X, h->scale, scratch, g);
+        LAUNCHED(h);
+        field = scratch + (size_t)grid_index * g.H * g.W;
+    }
+    const int sh = g.H < 16 ? g.H : 16, sw = g.W < 16 ? g.W : 16;       // centre sample, 16 x 16 on the reference's grid
+    const int oy = (g.H - sh) / 2, ox = (g.W - sw) / 2;
+    std::vector<float> sample((size_t)sh * sw), taps(NH * 9);
+    CK(h, cudaMemcpy2DAsync(sample.data(), sw * sizeof(float), field + (size_t)oy * g.W + ox, g.W * sizeof(float),
+                            sw * sizeof(float), sh, cudaMemcpyDeviceToHost, st));
+    CK(h, cudaMemcpyAsync(taps.data(), h->master + (size_t)set * MW_STRIDE + MW_K, taps.size() * sizeof(float),
+                          cudaMemcpyDeviceToHost, st));
+    CK(h, cudaStreamSynchronize(st));
+    std::string out;
+    char tmp[96];
+    auto put = [&](const char* fmt, auto... a) { snprintf(tmp, sizeof(tmp), fmt, a...); out += tmp; };
+    put("{\"gen\":%d,\"elapsed\":%.2f,", generation, elapsed_seconds);
+    out += "\"chemical\":{\"concentration\":[";
+    for (size_t i = 0; i < sample.size(); ++i) { put("%.4f", sample[i]); if (i + 1 < sample.size()) out += ","; }
+    put("],\"size\":%d},", sh < sw ? sh : sw);
+    out += "\"ca\":{\"flow_kernels\":[";
+    for (int hd = 0; hd < NH; ++hd) {
+        out += "[";
+        for (int t = 0; t < 9; ++t) { put("%.4f", taps[hd * 9 + t]); if (t < 8) out += ","; }
+        out += hd + 1 < NH ? "]," : "]";
+    }
+    out += "]},\"agents\":[],\"voronoi\":[],\"archive\":{\"size\":0,\"elites\":[]},";
+    put("\"pool\":{\"active\":%d,\"capacity\":%d,\"spawned\":%d,\"culled\":%d}", pool_active, pool_capacity,
+        pool_spawned, pool_culled);
+    out += "}\n";
+    if (written) *written = out.size();
+    if (out.size() + 1 > cap) return fail(h, SLIME_CA_EINVAL, "record needs " + std::to_string(out.size() + 1) + " bytes");
+    memcpy(buf, out.c_str(), out.size() + 1);
+    return SLIME_CA_OK;
+}
+
 void launch_multi_head_ca(float* ca_state, float* weights, float* ca_output, int batch_size, int grid_size) {
     static slime_ca* cached = nullptr;
     if (!ca_state || !weights || !ca_output || batch_size <= 0 || grid_size <= 0) {

@@ -102,3 +102,37 @@ def test_field_lift_and_write_back(dtype_name, tol):
         assert np.linalg.norm(got - ref) / np.linalg.norm(ref) < tol
         # and the channel mean of what get_state returns, up to summation order
         assert np.abs(got - ca_oracle.field_from_state(h.get_state())).max() < 2e-6 * np.abs(got).max() + 1e-7
+
+
+def test_evolution_record_line():
+    """The trajectory record has the reference file's keys, order and number formats, and carries the grid's
+    centre sample of the field and its weight set's flow kernels."""
+    import json
+    import torch
+    from oracle import ca_oracle
+    from slime_b200 import capi, inputs
+    B, H, W = 4, 32, 48
+    w = inputs.make_weight_sets(2, seed=3)
+    X0 = inputs.make_state(B, H, W, seed=3, scale=0.45 * H * W)
+    with capi.Handle(B, H, W, n_weight_sets=2, dtype=capi.F32) as h:
+        h.set_weights(w)
+        h.set_state(X0)
+        h.step(2)
+        line = h.evolution_record(3, 700, 12.3456, active=5, capacity=8, spawned=9, culled=4)
+        field = ca_oracle.field_from_state(h.get_state())[3]
+        # and from a field the caller holds on the device
+        mine = torch.arange(H * W, dtype=torch.float32, device="cuda").reshape(H, W) / 100.0
+        line2 = h.evolution_record(0, 1, 0.0, dev_field_ptr=mine.data_ptr())
+    assert line.endswith("}\n") and line.startswith('{"gen":700,"elapsed":12.35,"chemical":{"concentration":[')
+    rec = json.loads(line)
+    assert list(rec) == ["gen", "elapsed", "chemical", "ca", "agents", "voronoi", "archive", "pool"]
+    assert rec["chemical"]["size"] == 16 and len(rec["chemical"]["concentration"]) == 256
+    want = field[(H - 16) // 2:(H - 16) // 2 + 16, (W - 16) // 2:(W - 16) // 2 + 16].reshape(-1)
+    assert np.abs(np.array(rec["chemical"]["concentration"]) - want).max() < 1e-4
+    assert np.abs(np.array(rec["ca"]["flow_kernels"]) - w.K[1]).max() <= 5.1e-5      # grid 3 uses weight set 1; %.4f
+    assert rec["agents"] == [] and rec["voronoi"] == [] and rec["archive"] == {"size": 0, "elites": []}
+    assert rec["pool"] == {"active": 5, "capacity": 8, "spawned": 9, "culled": 4}
+    rec2 = json.loads(line2)
+    got2 = np.array(rec2["chemical"]["concentration"]).reshape(16, 16)
+    assert np.abs(got2 - mine.cpu().numpy()[8:24, 16:32]).max() < 1e-4
+    assert np.abs(np.array(rec2["ca"]["flow_kernels"]) - w.K[0]).max() <= 5.1e-5
