@@ -191,3 +191,36 @@ def test_torus_shift_equivariance_full_size(gpu):
             outs.append((devmem.state_view(h).float().cpu().numpy().reshape(B, H, W, 64), devmem.vprime(h, capi.BUF_VPRIME_LAST)))
     assert np.array_equal(np.roll(outs[0][1], (dy, dx), axis=(1, 2)), outs[1][1])
     assert np.array_equal(np.roll(outs[0][0], (dy, dx), axis=(1, 2)), outs[1][0])
+
+
+def test_two_handles_on_two_host_threads(gpu):
+    """Handles are independent: two host threads, each driving its own handle on its own stream on the same GPU,
+    get exactly what each handle gives when run alone."""
+    import threading
+    import torch
+    capi, _ = gpu
+    w = inputs.make_weight_sets(1, seed=8)
+    states = [inputs.make_state(6, 64, 48, seed=30 + i, scale=0.45 * 64 * 48) for i in range(2)]
+
+    def run(i, out, stream):
+        with capi.Handle(6, 64, 48, dtype=capi.BF16, keep_vprime=True) as h:
+            h.set_weights(w)
+            for _ in range(3):
+                h.set_state(states[i], stream=stream)
+                h.step(5, stream=stream)
+                fit = h.fitness(stream=stream)
+                out[i] = (h.get_state(stream=stream), fit["fitness"].copy())
+
+    alone = [None, None]
+    for i in range(2):
+        run(i, alone, 0)
+    streams = [torch.cuda.Stream() for _ in range(2)]
+    together = [None, None]
+    threads = [threading.Thread(target=run, args=(i, together, streams[i].cuda_stream)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    for i in range(2):
+        assert np.array_equal(alone[i][0], together[i][0])
+        assert np.array_equal(alone[i][1], together[i][1])
