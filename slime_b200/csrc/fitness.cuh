@@ -14,12 +14,17 @@ constexpr int JSTRIDE = 65;        // padded row stride of the Jacobi matrix in 
 
 // gram_part[((b*8+h)*splits + split)][64][64] (fp64) over cells [split*GRAM_CHUNK, ...) of plane (b,h).
 // The Gram matrix is symmetric: only the 136 4x4 blocks on or above the diagonal are accumulated (one thread
-// each, 160 threads per block) and each is written to both places.
+// each, 160 threads per block) and each is written to both places.  A chunk of 64 cells is converted to fp64
+// once, on its way into shared memory (the conversion is the slow instruction here: converting at the point of
+// use cost one conversion per two multiply-adds and made them the bottleneck).  Each 4-value block of a cell is
+// kept as two 16-byte halves in two planes, so a warp's loads of consecutive blocks are consecutive 16-byte
+// words: no bank conflicts.
 constexpr int GRAM_THREADS = 160;
 template <typename T>
 __global__ void __launch_bounds__(GRAM_THREADS)
 k_gram(const T* __restrict__ vp, int cells, double* __restrict__ gram_part) {
-    __shared__ __align__(16) float f[64][68];
+    __shared__ __align__(16) double2 flo[64][16];      // values 4 blk + 0, 4 blk + 1 of cell s
+    __shared__ __align__(16) double2 fhi[64][16];      // values 4 blk + 2, 4 blk + 3
     const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z, splits = gridDim.x;
     const T* plane = vp + ((size_t)b * NH + h) * (size_t)cells * HD;
     // thread t -> block (bi, bj), bi <= bj, rows of the upper triangle laid end to end: row bi starts at
@@ -27,7 +32,7 @@ k_gram(const T* __restrict__ vp, int cells, double* __restrict__ gram_part) {
     int bi = 0, rest = threadIdx.x;
     const bool live = threadIdx.x < 136;
     if (live) { while (rest >= 16 - bi) { rest -= 16 - bi; ++bi; } } else rest = 0;
-    const int ti = bi * 4, tj = (bi + rest) * 4;
+    const int bj = bi + rest, ti = bi * 4, tj = bj * 4;
     double acc[4][4];
 #pragma unroll
     for (int i = 0; i < 4; ++i)
@@ -37,18 +42,22 @@ k_gram(const T* __restrict__ vp, int cells, double* __restrict__ gram_part) {
     const int hi = min(lo + GRAM_CHUNK, cells);
     for (int s0 = lo; s0 < hi; s0 += 64) {
         __syncthreads();
-        for (int i = threadIdx.x; i < 64 * 64; i += GRAM_THREADS) {
-            const int s = s0 + (i >> 6);
-            f[i >> 6][i & 63] = s < hi ? to_f32<T>(plane[(size_t)s * HD + (i & 63)]) : 0.f;
+        for (int i = threadIdx.x; i < 64 * 32; i += GRAM_THREADS) {       // one pair of adjacent values per step
+            const int sl = i >> 5, pr = i & 31, s = s0 + sl;
+            double2 v = make_double2(0.0, 0.0);
+            if (s < hi) {
+                v.x = (double)to_f32<T>(plane[(size_t)s * HD + 2 * pr]);
+                v.y = (double)to_f32<T>(plane[(size_t)s * HD + 2 * pr + 1]);
+            }
+            if (pr & 1) fhi[sl][pr >> 1] = v; else flo[sl][pr >> 1] = v;
         }
         __syncthreads();
         if (live) {
 #pragma unroll 4
             for (int s = 0; s < 64; ++s) {
-                const float4 a = *reinterpret_cast<const float4*>(&f[s][ti]);
-                const float4 c = *reinterpret_cast<const float4*>(&f[s][tj]);
-                const double av[4] = {a.x, a.y, a.z, a.w};
-                const double cv[4] = {c.x, c.y, c.z, c.w};
+                const double2 a0 = flo[s][bi], a1 = fhi[s][bi], c0 = flo[s][bj], c1 = fhi[s][bj];
+                const double av[4] = {a0.x, a0.y, a1.x, a1.y};
+                const double cv[4] = {c0.x, c0.y, c1.x, c1.y};
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
 #pragma unroll
