@@ -86,39 +86,35 @@ __global__ void compute_effective_rank_kernel(float* __restrict__, float* __rest
     slime_compat_request.rank_slot = effective_rank;
 }
 
-// Weight initialisation with the reference's distributions (slime/core/pseudopod.cu:386-444): normal weights
-// scaled sqrt(2/(fan_in+fan_out)), sqrt(2/CHANNELS), sqrt(2/HIDDEN_DIM); mixing = identity + 0.01 N(0,1); flow
-// kernels uniform, each head's nine taps divided by their sum.  The random stream is a counter hash, not
-// curand's Philox: start states are statistically, not bitwise, those of the reference binary.
-__device__ __forceinline__ uint64_t slime_compat_mix(uint64_t z) {
-    z += 0x9e3779b97f4a7c15ull;
-    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
-    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
-    return z ^ (z >> 31);
-}
-__device__ __forceinline__ float slime_compat_uniform(uint64_t key) {   // (0, 1]
-    return ((float)(slime_compat_mix(key) >> 40) + 1.0f) * (1.0f / 16777216.0f);
-}
-__device__ __forceinline__ float slime_compat_normal(uint64_t key) {
-    const float u1 = slime_compat_uniform(2 * key), u2 = slime_compat_uniform(2 * key + 1);
-    return sqrtf(-2.0f * logf(u1)) * cosf(6.2831853f * u2);
+// Weight initialisation, bit-compatible with the reference's (slime/core/pseudopod.cu:386-444) when compiled with the
+// reference's flags: thread tid owns subsequence tid of cuRAND's default generator seeded with `seed` and draws, in
+// this order, one normal each for element tid of the perception, interaction and value arrays (scaled
+// sqrt(2/(fan_in+fan_out)), sqrt(2/CHANNELS), sqrt(2/HIDDEN_DIM)), one normal for mixing element tid < 64
+// (identity + 0.01 N) and one uniform for flow tap tid < 72.  The reference then lets threads 0..7 normalise their
+// head's nine taps by reading what threads 0..71 wrote, which nothing orders; here the thread of head h replays the
+// draws of its nine tap threads itself, so the taps are always the normalised ones.
+__device__ __forceinline__ float slime_compat_tap_draw(unsigned int seed, int t) {
+    curandState_t rng;
+    curand_init(seed, t, 0, &rng);
+    curand_normal(&rng); curand_normal(&rng); curand_normal(&rng);      // the three weight draws of thread t
+    if (t < NUM_HEADS * NUM_HEADS) curand_normal(&rng);                  // its mixing draw
+    return curand_uniform(&rng);
 }
 
 __global__ void init_multihead_ca_kernel(MultiHeadCAState* state, unsigned int seed) {
     const int tid = blockIdx.x * blockDim.x + threadIdx.x;
-    const int n_big = NUM_HEADS * CHANNELS * HIDDEN_DIM;
-    const uint64_t base = (uint64_t)seed << 34;
-    if (tid < n_big) {
-        state->perception_weights[tid] = slime_compat_normal(base + tid) * sqrtf(2.0f / (CHANNELS + HIDDEN_DIM));
-        state->interaction_weights[tid] = slime_compat_normal(base + n_big + tid) * sqrtf(2.0f / CHANNELS);
-        state->value_weights[tid] = slime_compat_normal(base + 2ull * n_big + tid) * sqrtf(2.0f / HIDDEN_DIM);
-    }
+    constexpr int n_big = NUM_HEADS * CHANNELS * HIDDEN_DIM;
+    if (tid >= n_big) return;
+    curandState_t rng;
+    curand_init(seed, tid, 0, &rng);
+    state->perception_weights[tid] = curand_normal(&rng) * sqrtf(2.0f / float(CHANNELS + HIDDEN_DIM));
+    state->interaction_weights[tid] = curand_normal(&rng) * sqrtf(2.0f / float(CHANNELS));
+    state->value_weights[tid] = curand_normal(&rng) * sqrtf(2.0f / float(HIDDEN_DIM));
     if (tid < NUM_HEADS * NUM_HEADS)
-        state->head_mixing_weights[tid] =
-            (tid / NUM_HEADS == tid % NUM_HEADS ? 1.0f : 0.0f) + 0.01f * slime_compat_normal(base + 3ull * n_big + tid);
-    if (tid < NUM_HEADS) {   // one thread per head draws and normalises its nine taps: no cross-thread ordering
+        state->head_mixing_weights[tid] = (tid / NUM_HEADS == tid % NUM_HEADS ? 1.0f : 0.0f) + curand_normal(&rng) * 0.01f;
+    if (tid < NUM_HEADS) {
         float taps[9], sum = 0.0f;
-        for (int t = 0; t < 9; ++t) { taps[t] = slime_compat_uniform(base + 4ull * n_big + tid * 9 + t); sum += taps[t]; }
+        for (int t = 0; t < 9; ++t) { taps[t] = slime_compat_tap_draw(seed, tid * 9 + t); sum += taps[t]; }
         for (int t = 0; t < 9; ++t) state->flow_kernels[tid * 9 + t] = taps[t] / sum;
     }
 }
