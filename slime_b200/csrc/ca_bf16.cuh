@@ -348,6 +348,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
             for (int h = 0; h < NH; ++h) {
                 const int i = k * NH + h, tb = i & 1;
                 const float mus = prm_e[h * PRM + 9];            // mu * s; Wp carries s and Wi carries log2(e)
+                const ptx::f2 neg_mus2 = ptx::make_f2(-mus, -mus), two2 = ptx::make_f2(2.f, 2.f), minus_one2 = ptx::make_f2(-1.f, -1.f);
                 ptx::mbar_wait(&tm_full[tb], (i >> 1) & 1, status, 140);
                 ptx::tc_fence_after();
                 const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16) + tb * 192;
@@ -362,14 +363,15 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                     ptx::tmem_ld_wait();
 #pragma unroll
                     for (int j = 0; j < 8; ++j) {
-                        float e2[2];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const float z = __uint_as_float(ru[2 * j + e]) - mus;
-                            const float gr = fmaf(2.f, ptx::ex2(-(z * z)), -1.f);
-                            e2[e] = ptx::ex2(fminf(fmaxf(gr * __uint_as_float(ri[2 * j + e]), -80.f * LOG2E), 80.f * LOG2E));
-                        }
-                        pe[sub][j] = pack_bf16(e2[0], e2[1]);
+                        // two elements at a time in packed fp32; only the two ex2 and the clamp are per element
+                        const ptx::f2 z = ptx::add2(ptx::make_f2(__uint_as_float(ru[2 * j]), __uint_as_float(ru[2 * j + 1])), neg_mus2);
+                        float q0, q1;
+                        ptx::split_f2(ptx::mul2(z, z), q0, q1);
+                        const ptx::f2 gr = ptx::fma2(ptx::make_f2(ptx::ex2(-q0), ptx::ex2(-q1)), two2, minus_one2);
+                        float a0, a1;
+                        ptx::split_f2(ptx::mul2(gr, ptx::make_f2(__uint_as_float(ri[2 * j]), __uint_as_float(ri[2 * j + 1]))), a0, a1);
+                        pe[sub][j] = pack_bf16(ptx::ex2(fminf(fmaxf(a0, -80.f * LOG2E), 80.f * LOG2E)),
+                                               ptx::ex2(fminf(fmaxf(a1, -80.f * LOG2E), 80.f * LOG2E)));
                         pv[sub][j] = pack_bf16(__uint_as_float(rv[2 * j]), __uint_as_float(rv[2 * j + 1]));
                     }
                 }
