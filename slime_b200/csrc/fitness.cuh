@@ -21,7 +21,7 @@ constexpr int JSTRIDE = 65;        // padded row stride of the Jacobi matrix in 
 // words: no bank conflicts.
 constexpr int GRAM_THREADS = 160;
 template <typename T>
-__global__ void __launch_bounds__(GRAM_THREADS)
+__global__ void __launch_bounds__(GRAM_THREADS, 6)
 k_gram(const T* __restrict__ vp, int cells, double* __restrict__ gram_part) {
     __shared__ __align__(16) double2 flo[64][16];      // values 4 blk + 0, 4 blk + 1 of cell s
     __shared__ __align__(16) double2 fhi[64][16];      // values 4 blk + 2, 4 blk + 3
@@ -53,7 +53,7 @@ k_gram(const T* __restrict__ vp, int cells, double* __restrict__ gram_part) {
         }
         __syncthreads();
         if (live) {
-#pragma unroll 4
+#pragma unroll 8
             for (int s = 0; s < 64; ++s) {
                 const double2 a0 = flo[s][bi], a1 = fhi[s][bi], c0 = flo[s][bj], c1 = fhi[s][bj];
                 const double av[4] = {a0.x, a0.y, a1.x, a1.y};
