@@ -82,7 +82,7 @@ class ClockSampler(threading.Thread):
 # capture is a batch of 8 grids (268 MB of E/V per kernel, larger than L2); traffic grows in proportion to the
 # cells, so a full launch is this figure times its cells.  k1's figure sits below its algorithmic bytes because
 # part of what it wrote was still dirty in the 126 MB L2 when the captured launch ended.
-NCU_DRAM_BYTES_PER_CELL = {"k1": (17.458e6 + 228.179e6) / 131072, "k2": (298.099e6 + 13.864e6) / 131072}
+NCU_DRAM_BYTES_PER_CELL = {"k1": (17.393e6 + 226.977e6) / 131072, "k2": (298.193e6 + 13.473e6) / 131072}
 
 
 def cpu_baseline(ca_steps_sample=2, grids=1):
