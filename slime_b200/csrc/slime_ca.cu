@@ -451,6 +451,7 @@ int slime_ca_step_timed(slime_ca* h, int n_steps, void* stream, float* ms) {
     std::vector<cudaEvent_t> ev((size_t)n_steps * 4);
     for (auto& e : ev) CK(h, cudaEventCreate(&e));
     const int n = h->g.B * NC;
+    h->vp_steps = 0; h->fitness_valid = false;      // these steps do not emit V': the kept pair no longer matches the state
     for (int i = 0; i < n_steps; ++i) {
         rc = step_kernels(h, nullptr, st, &ev[(size_t)i * 4]);
         if (rc) return rc;
