@@ -64,3 +64,24 @@ def test_oracle_field_from_state():
     rng = np.random.default_rng(4)
     X = rng.random((2, 5, 7, 64)).astype(np.float32)
     assert np.allclose(ca_oracle.field_from_state(X), X.astype(np.float64).mean(-1), atol=1e-7)
+
+
+def test_output_projection_folds_the_reference_head_mixing():
+    """tests/golden/ref_mix_heads.json holds what the reference's own mix_heads_kernel wrote on a B200 for six cells
+    (oracle/ref_mix_harness.cu, `make -C oracle ref_mix`).  The contract state has 64 channels where the reference's
+    mixed output has 8 x 64; slime_ca_set_weights_reference_layout folds the 8 x 8 mixing followed by the mean of the
+    eight output heads into Wo.  Applied to the same head outputs that Wo must give the mean of the reference
+    kernel's output heads."""
+    import json
+    ref = json.load(open(os.path.join(ROOT, "tests", "golden", "ref_mix_heads.json")))
+    f = lambda a: np.array(a, dtype=np.uint32).view(np.float32)
+    mix = f(ref["mixing"]).reshape(8, 8)
+    z = np.zeros((8, 512, 256), np.float32)
+    Wo = ca_oracle.weights_from_reference_layout(z, z, np.zeros((8, 256, 512), np.float32), mix, np.zeros((8, 9), np.float32))[3]
+    assert len(ref["cells"]) == 6
+    for cell in ref["cells"]:
+        v = f(cell["head_outputs"]).astype(np.float64)                   # [8 heads * 64]
+        out = f(cell["final_output"]).astype(np.float64).reshape(8, 64)  # [out_head][c]
+        # the reference kernel itself: out[o][c] = sum_in mixing[o][in] * v[in][c]
+        assert np.abs(out - mix.astype(np.float64) @ v.reshape(8, 64)).max() < 1e-6
+        assert np.abs(v @ Wo.astype(np.float64) - out.mean(axis=0)).max() < 1e-6
