@@ -5,9 +5,16 @@
 
 Workload (N=1 and every N, weak scaling: each rank steps its own batch, no data-path collective): the batched
 training-shape forward X[64,128,128,64], bf16 storage / fp32 accumulate, 8 heads x 64, 64 CA steps per bench
-step, seeded synthetic state (uniform, unit mass per channel) and one seeded weight set.  One bench "step" is
-one such 64-step forward.  `value` is timed with the state resident in HBM; `e2e` copies the state in from
-pinned host memory and back out through the C ABI inside the timed region.
+step, seeded synthetic state (uniform, unit mass per channel) and one seeded weight set (the specified draws with
+the output projection made mass-neutral, inputs.mass_neutral: with the plain draws the state grows 1.38x per step
+and overflows long before step 64).  One bench "step" is one such 64-step forward, started from the same state
+every time.  `value` is timed with the state resident in HBM (restored from a device copy at the start of every
+forward); `e2e` copies the state in from pinned host memory and back out through the C ABI inside the timed region.
+
+After that timing the line also gets a `stripe` object: one 8192 x 8192 torus split into N row stripes (strong
+scaling), 10 steps through the ring inside the C library (NCCL halo rows + all-reduce of the channel sums), with
+the per-step split between halo exchange, kernels and all-reduce, the mass error, and the parity of a small torus
+stepped as N stripes against rank 0 holding it whole.
 
 `--impl reference` times the CPU transcription of the same step (the reference has no CPU path and no runnable
 GPU step; the transcription is the oracle's fp32 build, all host threads) on a bounded sample of the workload.
@@ -77,12 +84,25 @@ class ClockSampler(threading.Thread):
                 "samples": len(self.rows)}
 
 
-# DRAM bytes per cell-update of each bf16 kernel, from the ncu captures summarised under profiles/
-# (k1_bf16_batch8_128x128.txt, k2_bf16_batch8_128x128.txt: dram__bytes_read.sum + dram__bytes_write.sum over 131 072 cells).  The
-# capture is a batch of 8 grids (268 MB of E/V per kernel, larger than L2); traffic grows in proportion to the
-# cells, so a full launch is this figure times its cells.  k1's figure sits below its algorithmic bytes because
-# part of what it wrote was still dirty in the 126 MB L2 when the captured launch ended.
-NCU_DRAM_BYTES_PER_CELL = {"k1": (17.393e6 + 226.977e6) / 131072, "k2": (298.193e6 + 13.473e6) / 131072}
+def ncu_dram_bytes_per_cell(kernel):
+    """DRAM bytes per cell-update of a bf16 kernel, read from the ncu summary committed under profiles/
+    (dram__bytes_read.sum + dram__bytes_write.sum of one captured launch over the cells of that launch).  The capture is
+    a batch of 8 grids (268 MB of E/V per kernel, larger than L2); traffic grows in proportion to the cells, so a full
+    launch is this figure times its cells.  k1's figure sits below its algorithmic bytes because part of what it wrote
+    was still dirty in the 126 MB L2 when the captured launch ended.  None if the summary is missing or unreadable."""
+    import re
+    path = os.path.join(ROOT, "profiles", f"{kernel}_bf16_batch8_128x128.txt")
+    try:
+        text = open(path).read()
+        cells = int(re.search(r"one launch = ([\d ]+) cells", text).group(1).replace(" ", ""))
+        unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+        total = 0.0
+        for name in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+            m = re.search(r"^" + re.escape(name) + r"\s+([\d.]+)\s+(\w+)", text, re.M)
+            total += float(m.group(1)) * unit[m.group(2)]
+        return total / cells
+    except (OSError, AttributeError, KeyError, ValueError):
+        return None
 
 
 def cpu_baseline(ca_steps_sample=2, grids=1):
@@ -90,7 +110,7 @@ def cpu_baseline(ca_steps_sample=2, grids=1):
     from oracle import ca_oracle
     from slime_b200 import inputs
     X = inputs.make_state(grids, GRID, GRID, seed=42)
-    w = inputs.make_weight_sets(1, seed=42)
+    w = inputs.make_weight_sets(1, seed=42, bounded=True)
     # all the host threads this process may use, whatever OMP_NUM_THREADS the launcher exported
     cores = ca_oracle.set_threads(ca_oracle.usable_cpus(), real="f32")
     ca_oracle.ca_steps(X[:1, :16, :16].copy(), w, 1, literal=False, real="f32")       # load + warm the library
@@ -136,6 +156,9 @@ def main():
     ap.add_argument("--batch", type=int, default=BATCH)
     ap.add_argument("--ca-steps", type=int, default=CA_STEPS)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-stripe", action="store_true", help="skip the row-stripe leg")
+    ap.add_argument("--stripe-edge", type=int, default=8192)
+    ap.add_argument("--stripe-steps", type=int, default=10)
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -160,11 +183,13 @@ def main():
     B, S = args.batch, args.ca_steps
     dt_code = capi.BF16 if args.dtype == "bf16" else capi.F32
     tdt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    weights = inputs.make_weight_sets(1, seed=42, bounded=True)
     h = capi.Handle(B, GRID, GRID, n_weight_sets=1, dtype=dt_code, device=local)
-    h.set_weights(inputs.make_weight_sets(1, seed=42))
+    h.set_weights(weights)
     X0 = inputs.make_state(B, GRID, GRID, seed=42, first_grid=rank * B)
     host = torch.from_numpy(X0).to(tdt).pin_memory()
     host_out = torch.empty_like(host).pin_memory()
+    dev0 = host.cuda()                       # the forward's start state, resident: restored before every forward
     state_bytes = host.numel() * host.element_size()
     stream = torch.cuda.current_stream().cuda_stream
     cells = B * GRID * GRID
@@ -189,30 +214,43 @@ def main():
             ms = float(t.item())
         return ms
 
-    # ---- device-resident throughput -------------------------------------------------------------
-    h.set_state_ptr(host.data_ptr(), dt_code, stream)
-    for _ in range(args.warmup):
+    # ---- device-resident throughput: every forward starts from the same resident state --------------
+    def forward():
+        h.set_state_device(dev0.data_ptr(), dt_code, stream)     # D2D restore + the masses of the start state
         h.step(S, stream)
+
+    for _ in range(args.warmup):
+        forward()
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:
         sampler.start()
     l0 = h.launch_count
-    ms = timed(lambda: h.step(S, stream), args.steps)
+    ms = timed(forward, args.steps)
     launches = h.launch_count - l0
     clocks = sampler.stop() if sampler else None
     value = world * cells * S * args.steps / (ms * 1e-3)
+    # what the last timed forward left: finite, and every channel's mass where it started
+    X_end = h.get_state(stream)
+    m0 = host.float().numpy().reshape(B, -1, 64).astype(np.float64).sum(1)
+    m1 = X_end.reshape(B, -1, 64).astype(np.float64).sum(1)
+    state_check = {"finite": bool(np.isfinite(X_end).all()), "max_mass_error": float(np.max(np.abs(m1 - m0) / np.abs(m0))),
+                   "max_abs_over_start": float(np.abs(X_end).max() / np.abs(X0).max())}
 
     # ---- per-kernel time of the same step loop (CUDA events between the kernels, on the launch stream) ----
+    h.set_state_device(dev0.data_ptr(), dt_code, stream)
     kt = h.step_timed(S, stream)          # ms summed over the S steps: k1, k2, reductions
     dom = "k1" if kt[0] >= kt[1] else "k2"
     dom_ms = max(kt[0], kt[1]) / S
     peak, tensor_peak, peak_kind = measured_peaks()
     achieved = cells * ALG_BYTES[dom][args.dtype] / (dom_ms * 1e-3) / 1e9
-    traffic = cells * NCU_DRAM_BYTES_PER_CELL[dom] if args.dtype == "bf16" else None
+    per_cell = ncu_dram_bytes_per_cell(dom) if args.dtype == "bf16" else None
     roofline = {"bound": "hbm", "kernel": dom + "_" + args.dtype, "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "traffic": traffic, "peak_kind": peak_kind,
+                "frac": achieved / peak, "traffic": None if per_cell is None else cells * per_cell, "peak_kind": peak_kind,
+                "traffic_source": f"profiles/{dom}_bf16_batch8_128x128.txt scaled by cells" if per_cell else None,
                 "algorithmic_bytes_per_launch": cells * ALG_BYTES[dom][args.dtype],
                 "ms_per_launch": dom_ms, "k1_ms": kt[0] / S, "k2_ms": kt[1] / S, "other_ms": kt[2] / S,
+                "k1_frac": cells * ALG_BYTES["k1"][args.dtype] / (kt[0] / S * 1e-3) / 1e9 / peak,
+                "k2_frac": cells * ALG_BYTES["k2"][args.dtype] / (kt[1] / S * 1e-3) / 1e9 / peak,
                 # the projections' 262 144 flop per cell-update over the whole step, against the sustained bf16 peak
                 # (the kernels run inside a long step loop): context, not the bound - the step is not tensor-bound
                 "tensor": {"achieved": cells * 262144 / ((kt[0] + kt[1] + kt[2]) / S * 1e-3) / 1e12, "peak": tensor_peak,
@@ -229,15 +267,11 @@ def main():
     ms_e2e = timed(e2e_step, args.steps)
     e2e = {"value": world * cells * S * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
            "h2d_bytes_per_step": state_bytes, "d2h_bytes_per_step": state_bytes}
-    # The specified generators make the step's zero-mean component grow about 1.3x per step (the oracle shows the
-    # same), so fp32 overflows between step 40 and 48; record how far the trajectory stays finite.
-    finite_after = {}
-    with capi.Handle(1, GRID, GRID, dtype=dt_code, device=local) as h1:
-        h1.set_weights(inputs.make_weight_sets(1, seed=42))
-        h1.set_state(X0[:1])
-        for k in (16, 32, 48, 64):
-            h1.step(16, stream)
-            finite_after[str(k)] = bool(np.isfinite(h1.get_state(stream)).all())
+    h.close()
+    del dev0
+    torch.cuda.empty_cache()
+
+    stripe = None if args.no_stripe else stripe_leg(args, rank, world, local, weights, timed)
 
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -245,17 +279,67 @@ def main():
                 "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
                 "config": {"workload": f"batched training-shape forward X[{B},{GRID},{GRID},64] per GPU, 8 heads x 64, "
                                        f"{S} CA steps per bench step, renorm every step",
+                           "weights": "specified draws, output projection made mass-neutral so the trajectory stays finite",
                            "l2": "working set per step (E,V intermediates %.1f GB) exceeds the 126 MB L2" %
                                  (2 * cells * 512 * (2 if args.dtype == "bf16" else 4) / 1e9),
                            "parallelism": f"batch-sharded x{world}, no data-path collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
-                "state_finite_after_steps": finite_after}
+                "state_after_last_timed_forward": state_check, "stripe": stripe}
         if not args.no_cpu_baseline and world == 1:       # the CPU baseline is timed at N = 1 only
             line["cpu_baseline"] = cpu_baseline(ca_steps_sample=CA_STEPS, grids=8)   # 8 of the 64 grids: 10-15 s
         print(json.dumps(line), flush=True)
-    h.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def stripe_leg(args, rank, world, local, weights, timed):
+    """The row-stripe split under the same launch: one torus, N stripes, the ring inside the C library."""
+    import torch
+    import torch.distributed as dist
+    from slime_b200 import capi, inputs, sharding, workloads
+
+    dt_code = capi.BF16 if args.dtype == "bf16" else capi.F32
+    edge, steps = args.stripe_edge, args.stripe_steps
+    out = {"workload": f"X[1,{edge},{edge},64] {args.dtype} torus as {world} row stripe(s), {steps} steps per timing, 3-row halo "
+                       "exchange (ncclSend/ncclRecv) + all-reduce of the 64 channel sums (fp64) every step, enqueued by "
+                       "slime_ca_step_ring with no host synchronisation per step", "scaling": "strong"}
+    # parity first, on a small torus: N stripes through the ring against rank 0 stepping the whole torus
+    H, W, psteps = 64, 48, 3
+    X0 = inputs.make_state(1, H, W, seed=8, scale=0.45 * H * W)
+    pw = inputs.make_weight_sets(1, seed=8)
+    small = sharding.StripedGrid(H, W, pw, dtype=dt_code, device=local)
+    small.load(X0[:, small.first_row:small.first_row + small.n_rows])
+    small.step(psteps)
+    small.handle.ring_wait(60000)
+    mine = torch.from_numpy(small.read()).cuda()
+    small.close()
+    if world > 1:
+        parts = [torch.empty_like(mine) for _ in range(world)] if rank == 0 else None
+        dist.gather(mine, parts, dst=0)
+    else:
+        parts = [mine]
+    if rank == 0:
+        with capi.Handle(1, H, W, dtype=dt_code, device=local) as whole:
+            whole.set_weights(pw); whole.set_state(X0); whole.step(psteps)
+            ref = whole.get_state()
+        got = torch.cat(parts, dim=1).cpu().numpy()
+        out["stripe_parity_rel_l2"] = float(np.linalg.norm(got.astype(np.float64) - ref) / np.linalg.norm(ref))
+        out["stripe_parity_case"] = f"{H}x{W} torus, {psteps} steps, {world} stripe(s) vs the whole torus on rank 0"
+    # the full-size torus
+    grid, mass = workloads.random_striped_grid(edge, args.dtype, rank, world, local, weights)
+    grid.step(2)
+    ms = timed(lambda: grid.step(steps), 1)
+    split = grid.handle.step_ring_timed(steps)
+    if world > 1:
+        t = torch.tensor(split, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        split = [float(v) for v in t.tolist()]
+    err = workloads.striped_mass_error(grid, mass)
+    grid.close()
+    out.update({"cell_updates_per_s": edge * edge * steps / (ms * 1e-3), "ms_per_step": ms / steps,
+                "ms_halo": split[0] / steps, "ms_kernels": split[1] / steps, "ms_allreduce": split[2] / steps,
+                "max_mass_error": err, "steps_before_mass_check": 2 + 2 * steps})
+    return out
 
 
 if __name__ == "__main__":

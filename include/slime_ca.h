@@ -29,7 +29,10 @@ enum slime_ca_status {
     SLIME_CA_ECUDA = 2,   /* a CUDA runtime call failed; slime_ca_last_error() has the text       */
     SLIME_CA_ENOMEM = 3,  /* host or device allocation failed                                     */
     SLIME_CA_ESTATE = 4,  /* call order: weights or state not set, fitness before two steps, ...  */
-    SLIME_CA_EDEVICE = 5  /* a kernel reported an error through its status word (bounded wait ran out) */
+    SLIME_CA_EDEVICE = 5, /* a kernel reported an error through its status word (bounded wait ran out);    */
+                          /* the state is undefined afterwards: load it again before further steps          */
+    SLIME_CA_ECOMM = 6,   /* the row-stripe ring's communicator (NCCL) failed or could not be loaded          */
+    SLIME_CA_ETIMEOUT = 7 /* slime_ca_ring_wait: the stream did not drain before the deadline               */
 };
 
 enum slime_ca_dtype {
@@ -82,6 +85,8 @@ size_t slime_ca_workspace_bytes(const slime_ca* h);
  *   Wp, Wi, Wv [8][64][64] = [head][c_in][d_out];  Wo [512][64] = [head*64+d][c_out];
  *   K [8][9] taps t=(dy+1)*3+(dx+1) (slime/core/pseudopod.cu:153);  mu, sigma [8] growth centre and width.
  * Replaces init_multihead_ca_kernel (slime/core/pseudopod.cu:386-444) as the way weights reach the device.
+ * Waits for the device to drain first (cudaDeviceSynchronize): steps in flight on any stream read the arrays this
+ * call overwrites.  Uploads run on the default stream and the call returns with them complete.
  */
 int slime_ca_set_weights(slime_ca* h, int set_index, const float* Wp, const float* Wi, const float* Wv,
                          const float* Wo, const float* K, const float* mu, const float* sigma);
@@ -95,7 +100,11 @@ int slime_ca_set_weights(slime_ca* h, int set_index, const float* Wp, const floa
 int slime_ca_set_state(slime_ca* h, const void* host_state, int host_dtype, void* stream);
 int slime_ca_get_state(slime_ca* h, void* host_state, int host_dtype, void* stream);
 
-/* Same with DEVICE pointers (no synchronisation). */
+/* Same with DEVICE pointers (no synchronisation).  A caller that never synchronises through this library
+ * (set_state_device / step / get_state_device on its own stream) still learns of a kernel that gave up on a
+ * bounded wait: every batch of steps copies the status word back to pinned host memory behind itself, and
+ * slime_ca_step, slime_ca_step_partial, slime_ca_step_ring and slime_ca_get_state_device return
+ * SLIME_CA_EDEVICE at their next call once that copy has run.  set_state_device clears the condition. */
 int slime_ca_set_state_device(slime_ca* h, const void* dev_state, int dtype, void* stream);
 int slime_ca_get_state_device(slime_ca* h, void* dev_state, int dtype, void* stream);
 
@@ -119,6 +128,41 @@ int slime_ca_step(slime_ca* h, int n_steps, void* stream);
  */
 int slime_ca_step_partial(slime_ca* h, void* stream);
 int slime_ca_step_finish(slime_ca* h, void* stream);
+
+/*
+ * Stripe mode, the ring inside the library: one torus split into row stripes, one handle (GPU, rank) per stripe,
+ * ranks forming a ring in y.  The reference has no multi-GPU code (one line of intent, BLUEPRINT.md:444-447;
+ * main.cu:12-13 selects device 0); this is the library's own answer for the large-grid workload.
+ *   slime_ca_ring_unique_id   rank 0 makes the 128-byte id (ncclGetUniqueId) and ships it to the other ranks by any
+ *                             means; slime_ca_ring_init(h, id, rank, world) is then called by every rank at the
+ *                             same time (ncclCommInitRank).  world = 1 needs no id and no NCCL: the stripe wraps
+ *                             onto itself.
+ *   slime_ca_ring_attach      the same with the caller's own ncclComm_t (passed as void*), which is not destroyed
+ *                             by the library.
+ *   slime_ca_ring_sync_mass   after loading every rank's own rows: sums the target masses over the ranks, so that
+ *                             each is the mass of the whole torus.
+ *   slime_ca_step_ring        n_steps steps, each: grouped ncclSend / ncclRecv of the 3 + 3 halo rows straight between
+ *                             the neighbours' state buffers, the step's kernels, ncclAllReduce of the 64 per-channel
+ *                             sums (fp64) of every grid, the new scale.  All of it is enqueued on `stream`; nothing
+ *                             synchronises with the host.  Kernels only ever read this GPU's own memory.
+ *   slime_ca_step_ring_timed  the same with CUDA events: ms[0] halo exchange, ms[1] the step's kernels and the local
+ *                             reduction, ms[2] all-reduce and scale, summed over the steps.  Synchronises.
+ *   slime_ca_ring_wait        bounded host wait for `stream` to drain: polls the stream and the communicator's
+ *                             asynchronous error state; on an NCCL error (SLIME_CA_ECOMM) or when timeout_ms runs out
+ *                             (SLIME_CA_ETIMEOUT) it aborts the communicator (ncclCommAbort) so that the stream ends,
+ *                             and the handle is left without a ring.  The reference's only error path is exit(1)
+ *                             (slime/runtime.cu:11-20).
+ * NCCL is bound at run time to the copy the process already carries, else to libnccl.so.2.
+ */
+#define SLIME_CA_RING_ID_BYTES 128
+int slime_ca_ring_unique_id(void* id_out);
+int slime_ca_ring_init(slime_ca* h, const void* id, int rank, int world);
+int slime_ca_ring_attach(slime_ca* h, void* nccl_comm, int rank, int world);
+int slime_ca_ring_detach(slime_ca* h);
+int slime_ca_ring_sync_mass(slime_ca* h, void* stream);
+int slime_ca_step_ring(slime_ca* h, int n_steps, void* stream);
+int slime_ca_step_ring_timed(slime_ca* h, int n_steps, void* stream, float* ms);
+int slime_ca_ring_wait(slime_ca* h, void* stream, int timeout_ms);
 
 /*
  * Profiling aid with no counterpart in the reference: n_steps steps with CUDA events recorded on `stream`
@@ -227,6 +271,39 @@ int slime_ca_evolution_record(slime_ca* h, int grid_index, int generation, doubl
                               const float* dev_field, int pool_active, int pool_capacity, int pool_spawned,
                               int pool_culled, char* buf, size_t cap, size_t* written, void* stream);
 
+/*
+ * The record the reference keeps of an elite (struct GPUElite, slime/memory/archive.cu:9-20, filled by
+ * create_elite_kernel :66-82) for one weight set, after slime_ca_fitness (and, for the parents, slime_ca_evolve):
+ * fitness, coherence and effective_rank are the means over the set's grids; genome_hash is the reference's hash
+ * (gpu_sha256, archive.cu:41-60) over the set's 131 168 fp32 master weights in upload order
+ * (Wp | Wi | Wv | Wo | K | mu | sigma); parent_ids name the set it was copied from at the last population step (itself
+ * for a survivor; both slots the same, the refill has one parent); generation is truncated to 16 bits as in the
+ * reference.  The behavioural coordinates, the compressed genome and the raw metrics of GPUElite belong to the
+ * archive, outside this library.  Synchronises `stream`.
+ */
+typedef struct slime_ca_elite {
+    float fitness;
+    float coherence;
+    float effective_rank;
+    unsigned long long genome_hash;
+    unsigned int parent_ids[2];
+    unsigned short generation;
+} slime_ca_elite;
+int slime_ca_elite_record(slime_ca* h, int set_index, int generation, slime_ca_elite* out, void* stream);
+
+/* Resident threads per SM of the step kernels of this handle's dtype over the SM's thread limit, from
+ * cudaOccupancyMaxActiveBlocksPerMultiprocessor (the smaller of the two kernels).  Backs
+ * KernelProtocol::theoretical_occupancy() (slime/proto/kernel.cu:14). */
+int slime_ca_occupancy(slime_ca* h, float* occupancy);
+
+/*
+ * Self-test of the bounded device-side waits, with no counterpart in the reference: launches one thread that waits
+ * `limit_ns` (at most 100 ms) on a barrier nobody arrives on, gives up, and records code 901 in the handle's status
+ * word.  The next synchronising call on the handle (or the next step call, once the word has been copied back)
+ * returns SLIME_CA_EDEVICE and clears the word; the context stays usable.
+ */
+int slime_ca_selftest_bounded_wait(slime_ca* h, unsigned long long limit_ns, void* stream);
+
 /* Number of kernels the library has launched on this handle since creation (for launch accounting). */
 long long slime_ca_launch_count(const slime_ca* h);
 
@@ -238,6 +315,9 @@ long long slime_ca_launch_count(const slime_ca* h);
  * Flow kernels are uniform (1/9 per tap) and the growth uses mu = 0.2, sigma = 0.03, the midpoints of the
  * ranges the weights are drawn from, because the planned signature carries neither.  Runs on the default
  * stream and synchronises.  Returns nothing, as planned; errors are printed to stderr.
+ * A shim: it keeps one handle in a function-local static (re-made when the shape or the device changes, never
+ * freed), so it is not safe to call from two host threads at once, and it passes the weights through the host on
+ * every call.  Code that steps repeatedly should hold a handle and call slime_ca_step.
  */
 void launch_multi_head_ca(float* ca_state, float* weights, float* ca_output, int batch_size, int grid_size);
 
@@ -253,7 +333,12 @@ void launch_multi_head_ca(float* ca_state, float* weights, float* ca_output, int
  *
  * Limit: batch * ceil(cells_per_grid / 256) <= 8192 (at most 2 097 152 cells per call); larger requests return
  * SLIME_CA_EINVAL and slime_ca_static_error() says so.  The first call on each device resolves the address of
- * the built-in array; make that first call outside any stream capture.  All calls on a device share the array,
+ * the built-in array; make that first call outside any stream capture, and make it early: once per device at
+ * start-up, before a memory pool takes the device and before the hot loop, because with lazy module loading that
+ * call may also be the one that loads the library's kernels and the array itself (which allocates and can
+ * synchronise).  The resolved address is cached per device ordinal for the life of the process: it is stale
+ * after cudaDeviceReset(), which this entry point does not survive.  Two host threads may make the first call on
+ * one device at once (they store the same address).  All calls on a device share the array,
  * which keeps whatever the last call left: nothing needs to start at zero (every slot a call reads it has
  * written first), but two calls whose kernels overlap on the GPU (different streams, different host threads)
  * race on it - run them one after the other.  Work is enqueued on `stream` of the CURRENT device; no

@@ -2,8 +2,12 @@
 //
 //   SlimePseudopod : ModelProtocol       forward(input, output) = one CA step on device fp32 buffers
 //                                        [batch][H][W][64]; effective_rank()/coherence() = results of the last
-//                                        compute_fitness().  The only protocol implementer the reference ever had
-//                                        is failed_attempts/model.cu:11-59 (Pseudopod : ModelProtocol).
+//                                        compute_fitness().  Chained calls - forward(a, b); forward(b, c); - continue
+//                                        the trajectory on the handle without reloading b, so the redistributed value
+//                                        of the last two steps stays paired and compute_fitness() works after two
+//                                        forwards (set chain_forward = false if b is modified between the calls).
+//                                        The only protocol implementer the reference ever had is
+//                                        failed_attempts/model.cu:11-59 (Pseudopod : ModelProtocol).
 //   SlimeComponent : ComponentProtocol   id / fitness / coherence / hunger bookkeeping around one SlimePseudopod
 //                                        (ComponentProtocol and ModelProtocol both name a `coherence` member, so
 //                                        one class can not derive from both without ambiguity).
@@ -27,7 +31,13 @@ public:
         gradients_d = nullptr;    // the CA is evolved, not trained by gradients
         num_parameters = n_weight_sets * (3 * 8 * 64 * 64 + 512 * 64 + 8 * 9 + 16);
         slime_ca_config cfg{batch, height, width, n_weight_sets, dtype, dt, device, 0, 1};
-        check(slime_ca_create(&cfg, &h_), "slime_ca_create");
+        const int rc = slime_ca_create(&cfg, &h_);
+        if (rc != SLIME_CA_OK) {
+            const std::string text = std::string("slime_ca_create: ") + slime_ca_last_error(h_);
+            if (h_) slime_ca_destroy(h_);     // create hands the handle back on failure so that the text can be read
+            h_ = nullptr;
+            throw std::runtime_error(text);
+        }
     }
     ~SlimePseudopod() { if (h_) slime_ca_destroy(h_); }
     SlimePseudopod(const SlimePseudopod&) = delete;
@@ -40,9 +50,11 @@ public:
 
     // ModelProtocol: device fp32 in, device fp32 out, one step
     void forward(float* input, float* output) override {
-        check(slime_ca_set_state_device(h_, input, SLIME_CA_F32, stream), "slime_ca_set_state_device");
+        if (!(chain_forward && input == last_output_))
+            check(slime_ca_set_state_device(h_, input, SLIME_CA_F32, stream), "slime_ca_set_state_device");
         check(slime_ca_step(h_, steps_per_forward, stream), "slime_ca_step");
         check(slime_ca_get_state_device(h_, output, SLIME_CA_F32, stream), "slime_ca_get_state_device");
+        last_output_ = output;
     }
     float effective_rank() override { return rank_; }
     float coherence() override { return coherence_; }
@@ -66,6 +78,7 @@ public:
 
     void* stream = nullptr;
     int steps_per_forward = 1;
+    bool chain_forward = true;      // forward(in, out) with in == the previous out continues without reloading
 
 private:
     static int batch_of(slime_ca* h) {
@@ -77,6 +90,7 @@ private:
         if (rc != SLIME_CA_OK) throw std::runtime_error(std::string(what) + ": " + slime_ca_last_error(h_));
     }
     slime_ca* h_ = nullptr;
+    const float* last_output_ = nullptr;
     float rank_ = 0.f, coherence_ = 0.f, fitness_ = 0.f, hunger_ = 1.f;
 };
 
@@ -114,8 +128,13 @@ public:
             throw std::runtime_error(slime_ca_last_error(model_->handle()));
     }
     size_t memory_required() const override { return slime_ca_workspace_bytes(model_->handle()); }
-    // resident threads per SM of the step kernels over the SM's 2048-thread limit (2 CTAs of 256-288 threads)
-    float theoretical_occupancy() const override { return 2.f * 256.f / 2048.f; }
+    // resident threads per SM of the handle's step kernels over the SM's thread limit, from the occupancy API
+    float theoretical_occupancy() const override {
+        float o = 0.f;
+        if (slime_ca_occupancy(model_->handle(), &o) != SLIME_CA_OK)
+            throw std::runtime_error(slime_ca_last_error(model_->handle()));
+        return o;
+    }
 
 private:
     SlimePseudopod* model_;

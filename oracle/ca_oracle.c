@@ -22,7 +22,10 @@
  *                   slime/core/pseudopod.cu:153,172-180 (tap order), slime/kernels/warp_ca.cu:305-306 (wrap)
  *   3 growth        G = 2 exp(-(U-mu)^2 / (2 sigma^2)) - 1
  *                   failed_attempts/warp_ca.cu:49-56, failed_attempts/pseudopod.cu:46-48
- *   4 activation    A = G * I                                  README.md:42-45
+ *   4 activation    A = clamp(G * I, -80, 80)                  README.md:42-45; the clamp is this step's
+ *                   domain limit: stages 5-6 are also evaluated in their closed form exp(A) / box3(exp(A)),
+ *                   which has no max-subtraction, and exp(80) keeps nine-term sums finite in fp32.  Inside
+ *                   |G I| <= 80 the clamp does nothing.  ORACLE_ACT_CLAMP below; oracle_set_activation_clamp().
  *   5 flow weights  source s sends to n in N(s) the share softmax_n(A(n)), max-subtracted
  *                   failed_attempts/pseudopod.cu:234-251, buildplan.md:608-622
  *   6 propagation   V'(n) = sum_{s in N(n)} w(s->n) V(s)        README.md:45-47 (sum out = sum in)
@@ -50,6 +53,10 @@ typedef ORACLE_REAL real;
 #define HD 64  /* head dim         slime/core/pseudopod.cu:16 */
 #define NC 64  /* state channels                              */
 #define HC (NH * HD)
+
+/* Bound on |A| (stage 4).  Part of the step's definition; the CUDA kernels use the same constant. */
+static double g_act_clamp = 80.0;
+double oracle_set_activation_clamp(double c) { const double old = g_act_clamp; if (c > 0) g_act_clamp = c; return old; }
 
 static inline real r_exp(real x) { return sizeof(real) == 4 ? (real)expf((float)x) : (real)exp((double)x); }
 
@@ -101,6 +108,7 @@ static void activation_head(const real* P, const real* I, int H, int W, const we
     const real mu = (real)w->mu[h];
     const real sg = (real)w->sigma[h];
     const real inv2s2 = (real)1 / ((real)2 * sg * sg);
+    const real clampv = (real)g_act_clamp;
 #pragma omp parallel for schedule(static)
     for (int y = 0; y < H; ++y) {
         for (int x = 0; x < W; ++x) {
@@ -116,7 +124,10 @@ static void activation_head(const real* P, const real* I, int H, int W, const we
             for (int d = 0; d < HD; ++d) {
                 const real z = u[d] - mu;
                 const real g = (real)2 * r_exp(-(z * z) * inv2s2) - (real)1;
-                A[o + d] = g * I[o + d];
+                real a = g * I[o + d];
+                if (a > clampv) a = clampv;
+                if (a < -clampv) a = -clampv;
+                A[o + d] = a;
             }
         }
     }
@@ -581,3 +592,24 @@ int oracle_set_threads(int n) {
 #endif
 }
 
+/*
+ * The reference's genome hash of an elite record (gpu_sha256, slime/memory/archive.cu:41-60; the name
+ * notwithstanding, a 64-bit shift-add-xor mix taken over the fp32 bit patterns in order).  Per value:
+ *   h ^= (bits + 0x9e3779b9 mod 2^32) + (h << 6) + (h >> 2);  h += h << 3;  h ^= h >> 11;  h += h << 15;
+ *   h *= 0xc4ceb9fe1a85ec53;  h ^= h >> 33;          starting from h = 0x9e3779b97f4a7c15.
+ * Pinned by tests/golden/ref_elite.json, which the reference's own create_elite_kernel wrote.
+ */
+unsigned long long oracle_genome_hash(const float* genome, unsigned long long n) {
+    uint64_t h = UINT64_C(0x9e3779b97f4a7c15);
+    for (unsigned long long i = 0; i < n; ++i) {
+        uint32_t bits;
+        memcpy(&bits, genome + i, 4);
+        h ^= (uint64_t)(uint32_t)(bits + UINT32_C(0x9e3779b9)) + (h << 6) + (h >> 2);   /* the 32-bit sum wraps, as in the reference's expression */
+        h += h << 3;
+        h ^= h >> 11;
+        h += h << 15;
+        h *= UINT64_C(0xc4ceb9fe1a85ec53);
+        h ^= h >> 33;
+    }
+    return (unsigned long long)h;
+}

@@ -53,6 +53,10 @@ def _lib(real: str):
         lib.oracle_field_from_state.argtypes = [_F, ctypes.c_int, ctypes.c_int, _F]
         lib.oracle_weights_from_reference_layout.restype = None
         lib.oracle_weights_from_reference_layout.argtypes = [_F] * 10
+        lib.oracle_set_activation_clamp.restype = ctypes.c_double
+        lib.oracle_set_activation_clamp.argtypes = [ctypes.c_double]
+        lib.oracle_genome_hash.restype = ctypes.c_ulonglong
+        lib.oracle_genome_hash.argtypes = [_F, ctypes.c_ulonglong]
         lib.oracle_set_threads.restype = ctypes.c_int
         lib.oracle_set_threads.argtypes = [ctypes.c_int]
         lib.oracle_evolve.restype = ctypes.c_int
@@ -186,6 +190,18 @@ def evolve(fit, weights, per_set, *, fitness_threshold, hunger_threshold, mutati
                                   parent.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), ctypes.byref(best))
     K, mu, sigma = K[parent], mu[parent], sigma[parent]      # taps, mu and sigma are inherited unchanged
     return (Wp, Wi, Wv, Wo, K, mu, sigma), parent, best.value, n
+
+
+def set_activation_clamp(c, real="f64"):
+    """Set the bound on |A| = |G * I| of one build of the oracle (80 by default, as in the CUDA kernels);
+    returns the previous bound.  Tests use a huge value to show where the clamp starts to act."""
+    return float(_lib(real).oracle_set_activation_clamp(float(c)))
+
+
+def genome_hash(genome):
+    """The reference's 64-bit genome hash over a flat fp32 array (bit patterns, in order)."""
+    g = _c32(genome).reshape(-1)
+    return int(_lib("f64").oracle_genome_hash(_f(g), g.size))
 
 
 def usable_cpus():

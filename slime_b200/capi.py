@@ -15,7 +15,8 @@ LIB_PATH = os.path.join(_HERE, "libslime_ca.so")
 
 F32, BF16 = 0, 1
 BUF_STATE, BUF_SCALE, BUF_MASS, BUF_SUMS, BUF_VPRIME_PREV, BUF_VPRIME_LAST = range(6)
-STATUS = {0: "OK", 1: "EINVAL", 2: "ECUDA", 3: "ENOMEM", 4: "ESTATE", 5: "EDEVICE"}
+STATUS = {0: "OK", 1: "EINVAL", 2: "ECUDA", 3: "ENOMEM", 4: "ESTATE", 5: "EDEVICE", 6: "ECOMM", 7: "ETIMEOUT"}
+RING_ID_BYTES = 128
 
 # every symbol include/slime_ca.h declares
 SYMBOLS = (
@@ -27,6 +28,9 @@ SYMBOLS = (
     "slime_ca_channel_sums_static", "slime_ca_static_error",
     "slime_ca_lift_field_device", "slime_ca_field_from_state_device", "slime_ca_set_weights_reference_layout",
     "slime_ca_get_weights", "slime_ca_evolve", "slime_ca_evolution_record",
+    "slime_ca_ring_unique_id", "slime_ca_ring_init", "slime_ca_ring_attach", "slime_ca_ring_detach",
+    "slime_ca_ring_sync_mass", "slime_ca_step_ring", "slime_ca_step_ring_timed", "slime_ca_ring_wait",
+    "slime_ca_elite_record", "slime_ca_occupancy", "slime_ca_selftest_bounded_wait",
 )
 
 
@@ -40,6 +44,11 @@ class Config(ctypes.Structure):
     _fields_ = [("batch", ctypes.c_int), ("height", ctypes.c_int), ("width", ctypes.c_int),
                 ("n_weight_sets", ctypes.c_int), ("dtype", ctypes.c_int), ("dt", ctypes.c_float),
                 ("device", ctypes.c_int), ("stripe", ctypes.c_int), ("keep_vprime", ctypes.c_int)]
+
+
+class Elite(ctypes.Structure):
+    _fields_ = [("fitness", ctypes.c_float), ("coherence", ctypes.c_float), ("effective_rank", ctypes.c_float),
+                ("genome_hash", ctypes.c_ulonglong), ("parent_ids", ctypes.c_uint * 2), ("generation", ctypes.c_ushort)]
 
 
 class EvolveParams(ctypes.Structure):
@@ -90,6 +99,17 @@ def lib():
                                                [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(ctypes.c_size_t), vp]
         L.slime_ca_launch_count.argtypes = [vp]
         L.slime_ca_launch_count.restype = ctypes.c_longlong
+        L.slime_ca_ring_unique_id.argtypes = [vp]
+        L.slime_ca_ring_init.argtypes = [vp, vp, ctypes.c_int, ctypes.c_int]
+        L.slime_ca_ring_attach.argtypes = [vp, vp, ctypes.c_int, ctypes.c_int]
+        L.slime_ca_ring_detach.argtypes = [vp]
+        L.slime_ca_ring_sync_mass.argtypes = [vp, vp]
+        L.slime_ca_step_ring.argtypes = [vp, ctypes.c_int, vp]
+        L.slime_ca_step_ring_timed.argtypes = [vp, ctypes.c_int, vp, fp]
+        L.slime_ca_ring_wait.argtypes = [vp, vp, ctypes.c_int]
+        L.slime_ca_elite_record.argtypes = [vp, ctypes.c_int, ctypes.c_int, ctypes.POINTER(Elite), vp]
+        L.slime_ca_occupancy.argtypes = [vp, fp]
+        L.slime_ca_selftest_bounded_wait.argtypes = [vp, ctypes.c_ulonglong, vp]
         L.launch_multi_head_ca.argtypes = [vp, vp, vp, ctypes.c_int, ctypes.c_int]
         L.launch_multi_head_ca.restype = None
         L.slime_ca_channel_sums_static.argtypes = [vp, ctypes.c_int, ctypes.c_int, ctypes.c_int, vp, vp]
@@ -105,6 +125,16 @@ def _fp(a):
 
 def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def ring_unique_id() -> bytes:
+    """The 128-byte id every rank of a row-stripe ring passes to Handle.ring_init (made on one rank, shipped to
+    the others by the caller)."""
+    buf = ctypes.create_string_buffer(RING_ID_BYTES)
+    rc = lib().slime_ca_ring_unique_id(buf)
+    if rc != 0:
+        raise SlimeCAError(rc, "slime_ca_ring_unique_id failed (is NCCL loadable?)")
+    return buf.raw
 
 
 class Handle:
@@ -216,6 +246,47 @@ class Handle:
         ms = np.zeros(3, np.float32)
         self._ck(lib().slime_ca_step_timed(self._h, int(n_steps), stream, _fp(ms)))
         return [float(x) for x in ms]
+
+    # -- row-stripe ring (stripe mode) ------------------------------------------------------------------
+    def ring_init(self, ring_id, rank, world):
+        """Join the ring: `ring_id` is the 128-byte id rank 0 got from ring_unique_id() (None when world == 1)."""
+        buf = None if ring_id is None else ctypes.create_string_buffer(bytes(ring_id), RING_ID_BYTES)
+        self._ck(lib().slime_ca_ring_init(self._h, buf, int(rank), int(world)))
+
+    def ring_detach(self):
+        self._ck(lib().slime_ca_ring_detach(self._h))
+
+    def ring_sync_mass(self, stream=0):
+        self._ck(lib().slime_ca_ring_sync_mass(self._h, stream))
+
+    def step_ring(self, n_steps=1, stream=0):
+        self._ck(lib().slime_ca_step_ring(self._h, int(n_steps), stream))
+
+    def step_ring_timed(self, n_steps, stream=0):
+        """-> [ms in the halo exchange, ms in the step's kernels, ms in the all-reduce + scale] summed over n_steps."""
+        ms = np.zeros(3, np.float32)
+        self._ck(lib().slime_ca_step_ring_timed(self._h, int(n_steps), stream, _fp(ms)))
+        return [float(x) for x in ms]
+
+    def ring_wait(self, timeout_ms, stream=0):
+        self._ck(lib().slime_ca_ring_wait(self._h, stream, int(timeout_ms)))
+
+    # -- records and diagnostics ---------------------------------------------------------------------------
+    def elite_record(self, set_index, generation, stream=0):
+        e = Elite()
+        self._ck(lib().slime_ca_elite_record(self._h, int(set_index), int(generation), ctypes.byref(e), stream))
+        return {"fitness": e.fitness, "coherence": e.coherence, "effective_rank": e.effective_rank,
+                "genome_hash": int(e.genome_hash), "parent_ids": (int(e.parent_ids[0]), int(e.parent_ids[1])),
+                "generation": int(e.generation)}
+
+    @property
+    def occupancy(self):
+        o = ctypes.c_float(0)
+        self._ck(lib().slime_ca_occupancy(self._h, ctypes.byref(o)))
+        return float(o.value)
+
+    def selftest_bounded_wait(self, limit_ns=1_000_000, stream=0):
+        self._ck(lib().slime_ca_selftest_bounded_wait(self._h, int(limit_ns), stream))
 
     def buffer(self, which):
         """-> (device address, bytes) of one of the handle's buffers."""

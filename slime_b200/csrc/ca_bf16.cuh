@@ -370,8 +370,8 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                         const ptx::f2 gr = ptx::fma2(ptx::make_f2(ptx::ex2(-q0), ptx::ex2(-q1)), two2, minus_one2);
                         float a0, a1;
                         ptx::split_f2(ptx::mul2(gr, ptx::make_f2(__uint_as_float(ri[2 * j]), __uint_as_float(ri[2 * j + 1]))), a0, a1);
-                        pe[sub][j] = pack_bf16(ptx::ex2(fminf(fmaxf(a0, -80.f * LOG2E), 80.f * LOG2E)),
-                                               ptx::ex2(fminf(fmaxf(a1, -80.f * LOG2E), 80.f * LOG2E)));
+                        pe[sub][j] = pack_bf16(ptx::ex2(fminf(fmaxf(a0, -ACT_CLAMP * LOG2E), ACT_CLAMP * LOG2E)),
+                                               ptx::ex2(fminf(fmaxf(a1, -ACT_CLAMP * LOG2E), ACT_CLAMP * LOG2E)));
                         pv[sub][j] = pack_bf16(__uint_as_float(rv[2 * j]), __uint_as_float(rv[2 * j + 1]));
                     }
                 }

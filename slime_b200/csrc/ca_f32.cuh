@@ -114,7 +114,7 @@ k1_f32(const float* __restrict__ X, const float* __restrict__ scale, const float
             for (int k = 0; k < 4; ++k) {
                 const float z = u[j][k] - mu;
                 const float gr = 2.f * expf(z * z * nis) - 1.f;
-                ep[k] = expf(gr * iv[j][k]);
+                ep[k] = expf(fminf(fmaxf(gr * iv[j][k], -ACT_CLAMP), ACT_CLAMP));
                 vp[k] = vv[j][k];
             }
             const size_t o = ((size_t)b * NH + h) * eplane + ((size_t)g.erow(r) * g.W + x) * HD + d0;

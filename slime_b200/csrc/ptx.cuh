@@ -41,8 +41,10 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
 }
 constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;   // one second of wall clock, then give up
 constexpr uint32_t WAIT_LIMIT_POLLS = 1u << 26;     // and never more than this many polls
-// Returns false (and records `code` in *status) if the phase did not complete within the limit.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+// Returns false (and records `code` in *status) if the phase did not complete within the limit (`limit_ns` of
+// wall clock; the step kernels use the default, the self-test a short one).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          uint64_t limit_ns = WAIT_LIMIT_NS) {
     uint64_t t0 = 0;
     for (uint32_t i = 0; i < WAIT_LIMIT_POLLS; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -50,7 +52,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
             if (*reinterpret_cast<volatile int*>(status) != 0) return false;   // a wait already failed: do not pile up
             const uint64_t t = globaltimer_ns();
             if (t0 == 0) t0 = t;
-            else if (t - t0 > WAIT_LIMIT_NS) break;
+            else if (t - t0 > limit_ns) break;
         }
     }
     atomicCAS(status, 0, code);

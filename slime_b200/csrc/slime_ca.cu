@@ -3,6 +3,7 @@
 // thread with dynamic parallelism is sequenced here from the host on one stream.
 #include "../../include/slime_ca.h"
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -16,6 +17,10 @@
 #include "common.cuh"
 #include "fitness.cuh"
 #include "evolve.cuh"
+#include "ring.cuh"
+
+#include <chrono>
+#include <thread>
 
 using namespace slime;
 
@@ -49,6 +54,7 @@ struct slime_ca {
     std::vector<char> weights_set;
     bool state_set = false;
     bool fitness_valid = false;     // fit_dev holds the fitness of the current V' pair
+    bool evolved = false;           // `parent` holds the result of a population step
     // fitness scratch
     double* gram_part = nullptr;
     int gram_splits = 0;
@@ -57,6 +63,12 @@ struct slime_ca {
     int pearson_splits = 0;
     float* fit_dev = nullptr;
     int* dev_status = nullptr;      // status word kernels with bounded waits report into
+    int* host_status = nullptr;     // pinned host mirror of it: copied back behind every batch of steps, read without
+                                    // synchronising at the start of the next call
+    // row-stripe ring (stripe mode): NCCL communicator over the ranks that hold the other stripes
+    void* comm = nullptr;
+    bool own_comm = false;
+    int ring_rank = 0, ring_world = 0;   // world 0 = no ring attached
     size_t bytes = 0;
     long long launches = 0;
     std::string err = "";
@@ -162,13 +174,95 @@ int ready(slime_ca* h) {
     return SLIME_CA_OK;
 }
 
+void ring_release(slime_ca* h) {
+    if (h->comm && h->own_comm && nccl::api().ok) nccl::api().CommDestroy((nccl::comm_t)h->comm);
+    h->comm = nullptr;
+    h->own_comm = false;
+    h->ring_world = 0;
+}
+
+#define NK(h, call)                                                                                         \
+    do {                                                                                                    \
+        int r_ = (call);                                                                                    \
+        if (r_ != nccl::SUCCESS)                                                                            \
+            return fail(h, SLIME_CA_ECOMM, std::string(#call) + ": " + nccl::describe(r_));                 \
+    } while (0)
+
+// Refresh the 3 + 3 halo rows of every grid's stripe from the ring neighbours' own rows (the step's dependency
+// radius is 3 rows).  Rows travel straight between the state buffers: my top own rows land in the upper
+// neighbour's bottom halo, my bottom own rows in the lower neighbour's top halo; with one rank the stripe wraps
+// onto itself by device copies.  Everything is enqueued on `st`; nothing synchronises.
+int ring_exchange(slime_ca* h, cudaStream_t st) {
+    const Geom& g = h->g;
+    const size_t row = (size_t)g.W * NC * h->esz, halo = 3 * row, plane = (size_t)g.state_rows() * row;
+    char* X = static_cast<char*>(h->X);
+    if (h->ring_world == 1) {
+        for (int b = 0; b < g.B; ++b) {
+            char* p = X + (size_t)b * plane;
+            CK(h, cudaMemcpyAsync(p, p + (size_t)g.H * row, halo, cudaMemcpyDeviceToDevice, st));                    // top halo <- bottom own
+            CK(h, cudaMemcpyAsync(p + (size_t)(g.H + 3) * row, p + 3 * row, halo, cudaMemcpyDeviceToDevice, st));    // bottom halo <- top own
+        }
+        return SLIME_CA_OK;
+    }
+    const nccl::Api& n = nccl::api();
+    nccl::comm_t comm = (nccl::comm_t)h->comm;
+    const int up = (h->ring_rank + h->ring_world - 1) % h->ring_world, down = (h->ring_rank + 1) % h->ring_world;
+    NK(h, n.GroupStart());
+    for (int b = 0; b < g.B; ++b) {
+        char* p = X + (size_t)b * plane;
+        // Sends and receives between one pair of ranks match in the order they are issued.  Every rank sends "top
+        // own rows up" before "bottom own rows down", so with two ranks (up == down) the peer's first message is
+        // its top rows, which belong in my bottom halo: receive the bottom halo first.
+        NK(h, n.Send(p + 3 * row, halo, nccl::DT_UINT8, up, comm, st));
+        NK(h, n.Send(p + (size_t)g.H * row, halo, nccl::DT_UINT8, down, comm, st));
+        NK(h, n.Recv(p + (size_t)(g.H + 3) * row, halo, nccl::DT_UINT8, down, comm, st));
+        NK(h, n.Recv(p, halo, nccl::DT_UINT8, up, comm, st));
+    }
+    NK(h, n.GroupEnd());
+    return SLIME_CA_OK;
+}
+
+int ring_allreduce(slime_ca* h, double* buf, cudaStream_t st) {
+    if (h->ring_world == 1) return SLIME_CA_OK;
+    const nccl::Api& n = nccl::api();
+    NK(h, n.AllReduce(buf, buf, (size_t)h->g.B * NC, nccl::DT_FLOAT64, nccl::OP_SUM, (nccl::comm_t)h->comm, st));
+    return SLIME_CA_OK;
+}
+
+int ring_ready(slime_ca* h) {
+    int rc = ready(h);
+    if (rc) return rc;
+    if (h->ring_world <= 0) return fail(h, SLIME_CA_ESTATE, "no ring attached: call slime_ca_ring_init or slime_ca_ring_attach first");
+    return SLIME_CA_OK;
+}
+
+const char* const AFTER_EDEVICE = "); the state is no longer defined: load it again before further steps";
+
+// After a synchronisation: read the device status word itself.
 int check_status_word(slime_ca* h) {
     int s = 0;
     CK(h, cudaMemcpy(&s, h->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (s != 0) {
         cudaMemset(h->dev_status, 0, sizeof(int));
-        return fail(h, SLIME_CA_EDEVICE, "a kernel gave up on a bounded wait (status word " + std::to_string(s) + ")");
+        *reinterpret_cast<volatile int*>(h->host_status) = 0;
+        return fail(h, SLIME_CA_EDEVICE, "a kernel gave up on a bounded wait (status word " + std::to_string(s) + AFTER_EDEVICE);
     }
+    return SLIME_CA_OK;
+}
+
+// Without synchronising: the mirror that the last batch of steps copied back, if that copy has run by now.  Lets a
+// caller that never leaves the device (set_state_device / step / get_state_device) learn of a failed wait at its
+// next call.
+int poll_status(slime_ca* h, cudaStream_t st) {
+    const int s = *reinterpret_cast<volatile int*>(h->host_status);
+    if (s == 0) return SLIME_CA_OK;
+    *reinterpret_cast<volatile int*>(h->host_status) = 0;
+    cudaMemsetAsync(h->dev_status, 0, sizeof(int), st);
+    return fail(h, SLIME_CA_EDEVICE, "a kernel of an earlier call gave up on a bounded wait (status word " + std::to_string(s) + AFTER_EDEVICE);
+}
+
+int publish_status(slime_ca* h, cudaStream_t st) {
+    CK(h, cudaMemcpyAsync(h->host_status, h->dev_status, sizeof(int), cudaMemcpyDeviceToHost, st));
     return SLIME_CA_OK;
 }
 
@@ -253,6 +347,8 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
     if ((rc = dev_alloc(h, &h->seg_sums, (size_t)g.B * 64 * NC))) return rc;
     if ((rc = dev_alloc(h, &h->dev_status, 1))) return rc;
     CK(h, cudaMemset(h->dev_status, 0, sizeof(int)));
+    CK(h, cudaHostAlloc((void**)&h->host_status, sizeof(int), cudaHostAllocDefault));
+    *h->host_status = 0;
     const size_t sets = cfg->n_weight_sets;
     if ((rc = dev_alloc(h, &h->prm, sets * NH * PRM))) return rc;
     if ((rc = dev_alloc(h, &h->master, sets * MW_STRIDE))) return rc;
@@ -283,6 +379,8 @@ int slime_ca_destroy(slime_ca* h) {
                     h->pearson_part, h->fit_dev, h->dev_status, h->master, h->set_stats, h->parent, h->evolve_info};
     for (void* p : ptrs)
         if (p) cudaFree(p);
+    if (h->host_status) cudaFreeHost(h->host_status);
+    ring_release(h);
     delete h;
     return SLIME_CA_OK;
 }
@@ -299,6 +397,9 @@ int slime_ca_set_weights(slime_ca* h, int set_index, const float* Wp, const floa
     for (int i = 0; i < NH; ++i)
         if (!(sigma[i] > 0.f)) return fail(h, SLIME_CA_EINVAL, "sigma must be positive");
     CK(h, cudaSetDevice(h->cfg.device));
+    // Steps still in flight on any stream (non-blocking streams are not ordered against the copies below) read the
+    // arrays this call overwrites: wait for the device to drain first.
+    CK(h, cudaDeviceSynchronize());
     // The fp32 master copy stays on the device (the population step mutates it there); the operand layouts of
     // the step kernels are derived from it by a kernel.
     float* m = h->master + (size_t)set_index * MW_STRIDE;
@@ -322,6 +423,10 @@ int slime_ca_set_state_device(slime_ca* h, const void* dev_state, int dtype, voi
     if (!dev_state || (dtype != SLIME_CA_F32 && dtype != SLIME_CA_BF16)) return fail(h, SLIME_CA_EINVAL, "bad state pointer or dtype");
     CK(h, cudaSetDevice(h->cfg.device));
     cudaStream_t st = (cudaStream_t)stream;
+    {
+        const int bad = *reinterpret_cast<volatile int*>(h->host_status);   // a fresh state ends an earlier failure
+        if (bad) { *reinterpret_cast<volatile int*>(h->host_status) = 0; cudaMemsetAsync(h->dev_status, 0, sizeof(int), st); }
+    }
     const Geom& g = h->g;
     const size_t n = (size_t)g.B * g.H * g.W * NC;
     const int blocks = grid_for(n);
@@ -346,6 +451,8 @@ int slime_ca_get_state_device(slime_ca* h, void* dev_state, int dtype, void* str
     if (!h->state_set) return fail(h, SLIME_CA_ESTATE, "no state has been loaded");
     CK(h, cudaSetDevice(h->cfg.device));
     cudaStream_t st = (cudaStream_t)stream;
+    int rcs = poll_status(h, st);
+    if (rcs) return rcs;
     const Geom& g = h->g;
     const int blocks = grid_for((size_t)g.B * g.H * g.W * NC);
     if (is_bf16(h)) {
@@ -405,12 +512,13 @@ int slime_ca_step_partial(slime_ca* h, void* stream) {
     int rc = ready(h);
     if (rc) return rc;
     CK(h, cudaSetDevice(h->cfg.device));
+    if ((rc = poll_status(h, (cudaStream_t)stream))) return rc;
     void* emit = nullptr;
     if (h->cfg.keep_vprime) { h->vp_last ^= 1; emit = h->vprime[h->vp_last]; ++h->vp_steps; h->fitness_valid = false; }
     rc = step_kernels(h, emit, (cudaStream_t)stream);
     if (rc) return rc;
     ++h->steps_done;
-    return SLIME_CA_OK;
+    return publish_status(h, (cudaStream_t)stream);
 }
 
 int slime_ca_step_finish(slime_ca* h, void* stream) {
@@ -429,6 +537,7 @@ int slime_ca_step(slime_ca* h, int n_steps, void* stream) {
     if (n_steps < 0) return fail(h, SLIME_CA_EINVAL, "negative step count");
     CK(h, cudaSetDevice(h->cfg.device));
     cudaStream_t st = (cudaStream_t)stream;
+    if ((rc = poll_status(h, st))) return rc;
     const int n = h->g.B * NC;
     for (int i = 0; i < n_steps; ++i) {
         void* emit = nullptr;
@@ -439,7 +548,7 @@ int slime_ca_step(slime_ca* h, int n_steps, void* stream) {
         LAUNCHED(h);
         ++h->steps_done;
     }
-    return SLIME_CA_OK;
+    return n_steps > 0 ? publish_status(h, st) : SLIME_CA_OK;
 }
 
 int slime_ca_step_timed(slime_ca* h, int n_steps, void* stream, float* ms) {
@@ -448,7 +557,12 @@ int slime_ca_step_timed(slime_ca* h, int n_steps, void* stream, float* ms) {
     if (n_steps <= 0 || n_steps > 4096 || !ms) return fail(h, SLIME_CA_EINVAL, "bad step count or null output");
     CK(h, cudaSetDevice(h->cfg.device));
     cudaStream_t st = (cudaStream_t)stream;
-    std::vector<cudaEvent_t> ev((size_t)n_steps * 4);
+    struct Events {          // destroyed on every way out of this function
+        std::vector<cudaEvent_t> v;
+        ~Events() { for (cudaEvent_t e : v) if (e) cudaEventDestroy(e); }
+    } evs;
+    evs.v.assign((size_t)n_steps * 4, nullptr);
+    std::vector<cudaEvent_t>& ev = evs.v;
     for (auto& e : ev) CK(h, cudaEventCreate(&e));
     const int n = h->g.B * NC;
     h->vp_steps = 0; h->fitness_valid = false;      // these steps do not emit V': the kept pair no longer matches the state
@@ -468,7 +582,6 @@ int slime_ca_step_timed(slime_ca* h, int n_steps, void* stream, float* ms) {
             CK(h, cudaEventElapsedTime(&t, ev[(size_t)i * 4 + k], ev[(size_t)i * 4 + k + 1]));
             ms[k] += t;
         }
-    for (auto& e : ev) cudaEventDestroy(e);
     return check_status_word(h);
 }
 
@@ -571,6 +684,7 @@ int slime_ca_evolve(slime_ca* h, const slime_ca_evolve_params* p, int* parent, i
     CK(h, cudaMemcpyAsync(info, h->evolve_info, sizeof(info), cudaMemcpyDeviceToHost, st));
     if (parent) CK(h, cudaMemcpyAsync(parent, h->parent, sets * sizeof(int), cudaMemcpyDeviceToHost, st));
     CK(h, cudaStreamSynchronize(st));
+    h->evolved = true;
     if (best_set) *best_set = info[0];
     if (n_replaced) *n_replaced = info[1];
     return SLIME_CA_OK;
@@ -604,6 +718,16 @@ int slime_ca_pool_readout(slime_ca* h, const float* host_Wr, const float* host_b
     if (!h) return SLIME_CA_EINVAL;
     if (!host_Wr || !host_logits || n_out <= 0 || n_out > 1024) return fail(h, SLIME_CA_EINVAL, "bad readout arguments");
     if (!h->state_set) return fail(h, SLIME_CA_ESTATE, "no state has been loaded");
+    {
+        // Wr, br and the logits are staged in the E intermediate (free between steps): they have to fit there
+        const Geom& g0 = h->g;
+        const size_t need = ((size_t)NC * n_out + n_out + (size_t)g0.B * n_out) * sizeof(float);
+        const size_t have = (size_t)g0.B * NH * g0.ev_h * g0.ev_w * HD * h->esz;
+        if (need > have)
+            return fail(h, SLIME_CA_EINVAL, "read-out too wide for this handle: (64 * n_out + n_out + batch * n_out) * 4 = " +
+                                                std::to_string(need) + " bytes exceed the " + std::to_string(have) +
+                                                "-byte staging buffer (batch * 8 * rows * columns * 64 elements)");
+    }
     CK(h, cudaSetDevice(h->cfg.device));
     cudaStream_t st = (cudaStream_t)stream;
     const Geom& g = h->g;
@@ -783,6 +907,269 @@ void launch_multi_head_ca(float* ca_state, float* weights, float* ca_output, int
 }  // extern "C"
 
 // ---------------------------------------------------------------------------------------------------------------
+// Row-stripe ring, occupancy, elite record, bounded-wait self-test.
+
+namespace {
+
+// The reference's genome hash (gpu_sha256, slime/memory/archive.cu:41-60: despite the name a 64-bit
+// shift-add-xor mix over the fp32 bit patterns, one value after the other), restated.
+unsigned long long genome_hash(const float* genome, size_t n) {
+    unsigned long long hsh = 0x9e3779b97f4a7c15ULL;
+    for (size_t i = 0; i < n; ++i) {
+        unsigned int bits;
+        memcpy(&bits, genome + i, sizeof bits);
+        hsh ^= (unsigned long long)(unsigned int)(bits + 0x9e3779b9u) + (hsh << 6) + (hsh >> 2);   // 32-bit sum, wrapping
+        hsh += hsh << 3;
+        hsh ^= hsh >> 11;
+        hsh += hsh << 15;
+        hsh *= 0xc4ceb9fe1a85ec53ULL;
+        hsh ^= hsh >> 33;
+    }
+    return hsh;
+}
+
+// One thread waits, with the limit it is given, on an mbarrier nobody will ever arrive on, and reports that.
+__global__ void k_wait_selftest(int* status, unsigned long long limit_ns, int code) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        ptx::fence_barrier_init();
+        ptx::mbar_wait(&bar, 0, status, code, limit_ns);
+        ptx::mbar_inval(&bar);
+    }
+}
+
+// n_steps ring steps; ev (optional) gets 4 events per step: before the exchange, after it, after the kernels and
+// the local reduction, after the all-reduce and the new scale
+int ring_steps(slime_ca* h, int n_steps, cudaStream_t st, std::vector<cudaEvent_t>* ev) {
+    const int n = h->g.B * NC;
+    for (int i = 0; i < n_steps; ++i) {
+        int rc;
+        if (ev) CK(h, cudaEventRecord((*ev)[(size_t)i * 4], st));
+        if ((rc = ring_exchange(h, st))) return rc;
+        if (ev) CK(h, cudaEventRecord((*ev)[(size_t)i * 4 + 1], st));
+        void* emit = nullptr;
+        if (h->cfg.keep_vprime && i >= n_steps - 2) { h->vp_last ^= 1; emit = h->vprime[h->vp_last]; ++h->vp_steps; h->fitness_valid = false; }
+        if ((rc = step_kernels(h, emit, st))) return rc;
+        if (ev) CK(h, cudaEventRecord((*ev)[(size_t)i * 4 + 2], st));
+        if ((rc = ring_allreduce(h, h->sums, st))) return rc;
+        k_scale_from_sums<<<(n + 255) / 256, 256, 0, st>>>(h->sums, h->mass, h->scale, n);
+        LAUNCHED(h);
+        if (ev) CK(h, cudaEventRecord((*ev)[(size_t)i * 4 + 3], st));
+        ++h->steps_done;
+    }
+    return SLIME_CA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int slime_ca_ring_unique_id(void* id_out) {
+    if (!id_out) return SLIME_CA_EINVAL;
+    const nccl::Api& n = nccl::api();
+    if (!n.ok) return SLIME_CA_ECOMM;
+    nccl::unique_id id;
+    if (n.GetUniqueId(&id) != nccl::SUCCESS) return SLIME_CA_ECOMM;
+    memcpy(id_out, &id, sizeof id);
+    return SLIME_CA_OK;
+}
+
+static int ring_check_handle(slime_ca* h, int rank, int world) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!h->cfg.stripe) return fail(h, SLIME_CA_ESTATE, "a ring needs a handle created in stripe mode");
+    if (world < 1 || rank < 0 || rank >= world) return fail(h, SLIME_CA_EINVAL, "bad rank or world size");
+    if (h->g.H < 3) return fail(h, SLIME_CA_EINVAL, "a stripe needs at least 3 own rows (the halo is 3 rows)");
+    return SLIME_CA_OK;
+}
+
+int slime_ca_ring_init(slime_ca* h, const void* id, int rank, int world) {
+    int rc = ring_check_handle(h, rank, world);
+    if (rc) return rc;
+    ring_release(h);
+    CK(h, cudaSetDevice(h->cfg.device));
+    if (world > 1) {
+        if (!id) return fail(h, SLIME_CA_EINVAL, "null unique id");
+        const nccl::Api& n = nccl::api();
+        if (!n.ok) return fail(h, SLIME_CA_ECOMM, n.error);
+        nccl::unique_id uid;
+        memcpy(&uid, id, sizeof uid);
+        nccl::comm_t comm = nullptr;
+        NK(h, n.CommInitRank(&comm, world, uid, rank));
+        h->comm = comm;
+        h->own_comm = true;
+    }
+    h->ring_rank = rank;
+    h->ring_world = world;
+    return SLIME_CA_OK;
+}
+
+int slime_ca_ring_attach(slime_ca* h, void* nccl_comm, int rank, int world) {
+    int rc = ring_check_handle(h, rank, world);
+    if (rc) return rc;
+    ring_release(h);
+    if (world > 1) {
+        if (!nccl_comm) return fail(h, SLIME_CA_EINVAL, "null communicator");
+        const nccl::Api& n = nccl::api();
+        if (!n.ok) return fail(h, SLIME_CA_ECOMM, n.error);
+        int count = 0, me = -1;
+        NK(h, n.CommCount((nccl::comm_t)nccl_comm, &count));
+        NK(h, n.CommUserRank((nccl::comm_t)nccl_comm, &me));
+        if (count != world || me != rank) return fail(h, SLIME_CA_EINVAL, "rank / world size do not match the communicator");
+        h->comm = nccl_comm;
+        h->own_comm = false;
+    }
+    h->ring_rank = rank;
+    h->ring_world = world;
+    return SLIME_CA_OK;
+}
+
+int slime_ca_ring_detach(slime_ca* h) {
+    if (!h) return SLIME_CA_EINVAL;
+    ring_release(h);
+    return SLIME_CA_OK;
+}
+
+int slime_ca_ring_sync_mass(slime_ca* h, void* stream) {
+    int rc = ring_ready(h);
+    if (rc) return rc;
+    CK(h, cudaSetDevice(h->cfg.device));
+    return ring_allreduce(h, h->mass, (cudaStream_t)stream);
+}
+
+int slime_ca_step_ring(slime_ca* h, int n_steps, void* stream) {
+    int rc = ring_ready(h);
+    if (rc) return rc;
+    if (n_steps < 0) return fail(h, SLIME_CA_EINVAL, "negative step count");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((rc = poll_status(h, st))) return rc;
+    if ((rc = ring_steps(h, n_steps, st, nullptr))) return rc;
+    return n_steps > 0 ? publish_status(h, st) : SLIME_CA_OK;
+}
+
+int slime_ca_step_ring_timed(slime_ca* h, int n_steps, void* stream, float* ms) {
+    int rc = ring_ready(h);
+    if (rc) return rc;
+    if (n_steps <= 0 || n_steps > 4096 || !ms) return fail(h, SLIME_CA_EINVAL, "bad step count or null output");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    struct Events {
+        std::vector<cudaEvent_t> v;
+        ~Events() { for (cudaEvent_t e : v) if (e) cudaEventDestroy(e); }
+    } evs;
+    evs.v.assign((size_t)n_steps * 4, nullptr);
+    for (auto& e : evs.v) CK(h, cudaEventCreate(&e));
+    if ((rc = ring_steps(h, n_steps, st, &evs.v))) return rc;
+    CK(h, cudaStreamSynchronize(st));
+    ms[0] = ms[1] = ms[2] = 0.f;
+    for (int i = 0; i < n_steps; ++i)
+        for (int k = 0; k < 3; ++k) {
+            float t = 0.f;
+            CK(h, cudaEventElapsedTime(&t, evs.v[(size_t)i * 4 + k], evs.v[(size_t)i * 4 + k + 1]));
+            ms[k] += t;
+        }
+    return check_status_word(h);
+}
+
+int slime_ca_ring_wait(slime_ca* h, void* stream, int timeout_ms) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (timeout_ms < 0) return fail(h, SLIME_CA_EINVAL, "negative timeout");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+    for (;;) {
+        const cudaError_t q = cudaStreamQuery(st);
+        if (q == cudaSuccess) return check_status_word(h);
+        if (q != cudaErrorNotReady) return fail(h, SLIME_CA_ECUDA, std::string("cudaStreamQuery: ") + cudaGetErrorString(q));
+        if (h->comm) {
+            int async = nccl::SUCCESS;
+            const nccl::Api& n = nccl::api();
+            if (n.CommGetAsyncError((nccl::comm_t)h->comm, &async) == nccl::SUCCESS && async != nccl::SUCCESS &&
+                async != nccl::IN_PROGRESS) {
+                n.CommAbort((nccl::comm_t)h->comm);      // frees the communicator and ends its kernels
+                h->comm = nullptr; h->own_comm = false; h->ring_world = 0;
+                return fail(h, SLIME_CA_ECOMM, "the ring's communicator reported " + nccl::describe(async) + "; it was aborted");
+            }
+        }
+        if (std::chrono::steady_clock::now() >= deadline) {
+            if (h->comm) {
+                nccl::api().CommAbort((nccl::comm_t)h->comm);
+                h->comm = nullptr; h->own_comm = false; h->ring_world = 0;
+                return fail(h, SLIME_CA_ETIMEOUT, "the stream did not drain within " + std::to_string(timeout_ms) +
+                                                      " ms; the ring's communicator was aborted (attach a new one to go on)");
+            }
+            return fail(h, SLIME_CA_ETIMEOUT, "the stream did not drain within " + std::to_string(timeout_ms) + " ms");
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+}
+
+int slime_ca_selftest_bounded_wait(slime_ca* h, unsigned long long limit_ns, void* stream) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (limit_ns == 0 || limit_ns > 100000000ull) return fail(h, SLIME_CA_EINVAL, "limit must lie in (0, 100 ms]");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    k_wait_selftest<<<1, 32, 0, st>>>(h->dev_status, limit_ns, 901);
+    LAUNCHED(h);
+    return publish_status(h, st);
+}
+
+int slime_ca_occupancy(slime_ca* h, float* occupancy) {
+    if (!h) return SLIME_CA_EINVAL;
+    if (!occupancy) return fail(h, SLIME_CA_EINVAL, "null output pointer");
+    CK(h, cudaSetDevice(h->cfg.device));
+    int max_threads = 0;
+    CK(h, cudaDeviceGetAttribute(&max_threads, cudaDevAttrMaxThreadsPerMultiProcessor, h->cfg.device));
+    int b1 = 0, b2 = 0, t1, t2;
+    if (is_bf16(h)) {
+        t1 = k1b::THREADS; t2 = k2b::THREADS;
+        if (h->bf.k1_aligned) CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b1, k1_bf16<true>, t1, k1b::SMEM));
+        else CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b1, k1_bf16<false>, t1, k1b::SMEM));
+        CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b2, k2_bf16, t2, k2b::SMEM));
+    } else {
+        t1 = t2 = 256;
+        CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b1, k1_f32, t1, K1F32_SMEM));
+        CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b2, k2_f32, t2, K2F32_SMEM));
+    }
+    const float o1 = (float)(b1 * t1) / (float)max_threads, o2 = (float)(b2 * t2) / (float)max_threads;
+    *occupancy = o1 < o2 ? o1 : o2;
+    return SLIME_CA_OK;
+}
+
+int slime_ca_elite_record(slime_ca* h, int set_index, int generation, slime_ca_elite* out, void* stream) {
+    int rc = ready(h);
+    if (rc) return rc;
+    if (!out) return fail(h, SLIME_CA_EINVAL, "null output pointer");
+    if (set_index < 0 || set_index >= h->cfg.n_weight_sets) return fail(h, SLIME_CA_EINVAL, "weight set index out of range");
+    if (!h->cfg.keep_vprime || !h->fitness_valid)
+        return fail(h, SLIME_CA_ESTATE, "the elite record follows slime_ca_fitness on the same state");
+    CK(h, cudaSetDevice(h->cfg.device));
+    cudaStream_t st = (cudaStream_t)stream;
+    const int per = h->g.per_set;
+    std::vector<float> fit((size_t)per * 4), genome(MW_STRIDE);
+    int parent = set_index;
+    CK(h, cudaMemcpyAsync(fit.data(), h->fit_dev + (size_t)set_index * per * 4, fit.size() * sizeof(float), cudaMemcpyDeviceToHost, st));
+    CK(h, cudaMemcpyAsync(genome.data(), h->master + (size_t)set_index * MW_STRIDE, genome.size() * sizeof(float), cudaMemcpyDeviceToHost, st));
+    CK(h, cudaMemcpyAsync(&parent, h->parent + set_index, sizeof(int), cudaMemcpyDeviceToHost, st));
+    CK(h, cudaStreamSynchronize(st));
+    double s[3] = {0, 0, 0};
+    for (int i = 0; i < per; ++i) { s[0] += fit[i * 4 + 2]; s[1] += fit[i * 4 + 1]; s[2] += fit[i * 4 + 0]; }
+    memset(out, 0, sizeof *out);
+    out->fitness = (float)(s[0] / per);
+    out->coherence = (float)(s[1] / per);
+    out->effective_rank = (float)(s[2] / per);
+    out->genome_hash = genome_hash(genome.data(), genome.size());
+    const unsigned int par = h->evolved ? (unsigned int)parent : (unsigned int)set_index;
+    out->parent_ids[0] = par;
+    out->parent_ids[1] = par;          // refills copy one parent (no crossover): both slots name it
+    out->generation = (unsigned short)(generation & 0xffff);
+    return SLIME_CA_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
 // Per-channel sums without any allocation.
 //
 // Some callers of this library can not allocate device memory at the point where they need a state's channel
@@ -800,7 +1187,7 @@ static __device__ __align__(256) float g_static_partials[(size_t)STATIC_MAX_CHUN
 
 namespace {
 constexpr int STATIC_MAX_DEVICES = 64;
-float* g_static_partials_addr[STATIC_MAX_DEVICES] = {};
+std::atomic<float*> g_static_partials_addr[STATIC_MAX_DEVICES] = {};
 thread_local std::string g_static_error;
 
 int static_fail(int code, const std::string& msg) {
@@ -827,14 +1214,14 @@ int slime_ca_channel_sums_static(const void* dev_state, int dtype, int batch, in
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return static_fail(SLIME_CA_ECUDA, std::string("cudaGetDevice: ") + cudaGetErrorString(e));
     if (dev < 0 || dev >= STATIC_MAX_DEVICES) return static_fail(SLIME_CA_EINVAL, "device ordinal out of range");
-    if (!g_static_partials_addr[dev]) {
+    if (!g_static_partials_addr[dev].load(std::memory_order_acquire)) {
         // set-up, once per device, with that device current: resolve the device address of the scratch array
         float* p = nullptr;
         e = cudaGetSymbolAddress((void**)&p, g_static_partials);
         if (e != cudaSuccess || !p) return static_fail(SLIME_CA_ECUDA, std::string("cudaGetSymbolAddress: ") + cudaGetErrorString(e));
-        g_static_partials_addr[dev] = p;
+        g_static_partials_addr[dev].store(p, std::memory_order_release);   // two first callers store the same address
     }
-    float* partial = g_static_partials_addr[dev];
+    float* partial = g_static_partials_addr[dev].load(std::memory_order_acquire);
     cudaStream_t st = (cudaStream_t)stream;
     Geom g{};
     g.B = batch; g.H = cells_per_grid; g.W = 1; g.hx = 0; g.he = 0; g.wrap_y = 1; g.per_set = 1;

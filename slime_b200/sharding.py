@@ -5,13 +5,18 @@ Two ways the path shards:
     collective on the data path (`shard_population`);
   * one large torus split into row stripes: every step each rank sends its 3 top and 3 bottom own rows to its
     ring neighbours (the step's dependency radius is 3: stencil 1 + softmax denominator 1 + gather 1) and the
-    64 per-channel sums are all-reduced for the global mass renormalisation (`StripeRing`, `StripedGrid`).
+    64 per-channel sums are all-reduced for the global mass renormalisation.  On GPUs the ring lives inside the C
+    library (slime_ca_step_ring: grouped ncclSend / ncclRecv and ncclAllReduce on the caller's stream, no host
+    synchronisation per step) and `StripedGrid` only sets it up; `StripeRing` is the same exchange over any
+    torch.distributed backend, which is what the CPU tests drive over gloo, with a deadline on every wait.
     Halo rows land in the receiver's own state buffer first; kernels only ever read local memory.
 
 The reference has no multi-GPU code (one line of intent: BLUEPRINT.md:444-447, device = hash % num_gpus).
 """
 from __future__ import annotations
 
+import datetime
+import time
 from dataclasses import dataclass
 
 import torch
@@ -53,11 +58,18 @@ def stripe_rows(height: int, rank: int, world: int):
     return rank * n, n
 
 
-class StripeRing:
-    """Halo exchange and sum reduction for one stripe per rank, ranks forming a ring in y (toroidal wrap)."""
+class RingTimeout(RuntimeError):
+    """A neighbour's halo rows (or the sum reduction) did not arrive within the ring's deadline."""
 
-    def __init__(self, group=None):
+
+class StripeRing:
+    """Halo exchange and sum reduction for one stripe per rank, ranks forming a ring in y (toroidal wrap).
+    Every wait is bounded by `timeout_s`: a neighbour that never sends raises RingTimeout instead of blocking
+    the rank for ever."""
+
+    def __init__(self, group=None, timeout_s: float = 60.0):
         self.group = group
+        self.timeout_s = float(timeout_s)
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.up = (self.rank - 1) % self.world        # owner of the rows above mine
@@ -82,21 +94,38 @@ class StripeRing:
                dist.P2POp(dist.irecv, recv_bot, self.down, self.group, tag=1)]
         if self.world == 2 and self.rank == 1:      # pair the operations in the same order on both ranks
             ops = [ops[1], ops[0], ops[3], ops[2]]
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
+        self._wait_all(dist.batch_isend_irecv(ops), "halo rows")
         top_halo.copy_(recv_top)
         bot_halo.copy_(recv_bot)
+
+    def _wait_all(self, reqs, what: str) -> None:
+        deadline = time.monotonic() + self.timeout_s
+        for i, r in enumerate(reqs):
+            left = max(deadline - time.monotonic(), 1e-3)
+            try:
+                ok = r.wait(datetime.timedelta(seconds=left))
+            except RuntimeError as e:           # gloo reports an expired wait as a RuntimeError
+                if "ime" not in str(e):         # "Timed out" / "timeout"
+                    raise
+                ok = False
+            if ok is False:
+                raise RingTimeout(f"rank {self.rank}: {len(reqs) - i} transfer(s) of {what} still pending after "
+                                  f"{self.timeout_s:g} s (neighbours {self.up}, {self.down})")
 
     def allreduce_sums(self, sums: torch.Tensor) -> None:
         """In-place sum over ranks of the [B][64] fp64 per-channel sums."""
         if self.world > 1:
-            dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=self.group)
+            self._wait_all([dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=self.group, async_op=True)], "channel sums")
 
 
 class StripedGrid:
-    """One large torus [1][H][W][64] stepped as row stripes, one per rank (GPU)."""
+    """One large torus [1][H][W][64] stepped as row stripes, one per rank (GPU).
 
-    def __init__(self, height, width, weights, *, dtype, device, group=None, dt=0.1):
+    `library_ring=True` (the default) joins the C library's own NCCL ring: the id made on rank 0 is broadcast over
+    `group`, and every step then runs inside slime_ca_step_ring with no host synchronisation.  `library_ring=False`
+    drives the same step from Python (StripeRing over torch.distributed around step_partial / step_finish)."""
+
+    def __init__(self, height, width, weights, *, dtype, device, group=None, dt=0.1, library_ring=True):
         from . import capi, devmem
         self.ring = StripeRing(group)
         self.first_row, self.n_rows = stripe_rows(height, self.ring.rank, self.ring.world)
@@ -104,15 +133,34 @@ class StripedGrid:
         self.handle.set_weights(weights)
         self.state = devmem.state_view(self.handle)
         self.sums = devmem.sums_view(self.handle)
+        self.library_ring = bool(library_ring)
+        if self.library_ring:
+            ring_id = None
+            if self.ring.world > 1:
+                box = [capi.ring_unique_id() if self.ring.rank == 0 else None]
+                dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+                ring_id = box[0]
+            self.handle.ring_init(ring_id, self.ring.rank, self.ring.world)
 
     def load(self, stripe_state) -> None:
         """stripe_state: this rank's own rows [1][n_rows][W][64] (host fp32); target masses are global sums."""
         self.handle.set_state(stripe_state)
+        self.adopt_masses()
+
+    def adopt_masses(self) -> None:
+        """Make the target masses those of the whole torus (sum over the ranks of what each stripe recorded)."""
+        if self.library_ring:
+            self.handle.ring_sync_mass()
+            torch.cuda.synchronize()
+            return
         mass = torch.from_numpy(self.handle.get_mass()).to(self.sums.device)
         self.ring.allreduce_sums(mass)
         self.handle.set_mass(mass.cpu().numpy())
 
     def step(self, n_steps: int = 1, stream: int = 0) -> None:
+        if self.library_ring:
+            self.handle.step_ring(n_steps, stream)
+            return
         for _ in range(n_steps):
             self.ring.exchange_halos(self.state, self.n_rows)
             self.handle.step_partial(stream)

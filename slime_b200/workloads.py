@@ -72,7 +72,7 @@ def config3(args, rank, world, local):
     n_grids, n_sets, steps = 1024 // args.scale_down, 128 // args.scale_down, 32
     sh = sharding.shard_population(n_grids, n_sets, rank, world)
     dt = capi.BF16 if args.dtype == "bf16" else capi.F32
-    w = inputs.make_weight_sets(sh.n_sets, seed=42, first_set=sh.first_set)
+    w = inputs.make_weight_sets(sh.n_sets, seed=42, first_set=sh.first_set, bounded=True)
     h = capi.Handle(sh.n_grids, 128, 128, n_weight_sets=sh.n_sets, dtype=dt, device=local, keep_vprime=True)
     h.set_weights(w)
     stage = torch.empty((sh.n_grids, 128, 128, 64), dtype=torch.float32).pin_memory()
@@ -108,15 +108,16 @@ def config3(args, rank, world, local):
             "finite_fraction": float(local_stats[2]), "scaling": "strong (1024 grids split over the ranks)"}
 
 
-def config4(args, rank, world, local):
-    edge, steps = 8192 // args.scale_down, 100
-    dt = capi.BF16 if args.dtype == "bf16" else capi.F32
-    w = inputs.make_weight_sets(1, seed=42)
-    grid = sharding.StripedGrid(edge, edge, w, dtype=dt, device=local)
-    # The 4.3e9-element state is drawn on the device (uniform, then unit mass per channel): throughput does not
-    # depend on the values, and the seeded host generator would need minutes and tens of GB for this size.
+def random_striped_grid(edge, dtype_name, rank, world, local, weights):
+    """One edge x edge torus split into `world` row stripes, this rank's stripe filled on the device with a uniform
+    state of unit mass per channel (seeded per rank) and adopted as the state; -> (StripedGrid, target masses).
+
+    The state of the full-size torus (4.3e9 elements) is drawn on the device: throughput does not depend on the
+    values, and the seeded host generator would need minutes and tens of GB for this size."""
+    dt = capi.BF16 if dtype_name == "bf16" else capi.F32
+    grid = sharding.StripedGrid(edge, edge, weights, dtype=dt, device=local)
     gen = torch.Generator(device="cuda").manual_seed(42 + rank)
-    tdt = torch.bfloat16 if args.dtype == "bf16" else torch.float32
+    tdt = torch.bfloat16 if dtype_name == "bf16" else torch.float32
     own = grid.state[:, sharding.HALO:sharding.HALO + grid.n_rows]
     for r0 in range(0, grid.n_rows, 256):
         blk = own[:, r0:r0 + 256]
@@ -130,27 +131,41 @@ def config4(args, rank, world, local):
         blk.copy_((blk.float() / sums.float().view(1, 1, 1, 64)).to(tdt))
     # adopt what is now stored as the state: masses from the stored values, summed over ranks
     grid.handle.set_state_device(own.contiguous().data_ptr(), dt)
+    grid.adopt_masses()
     mass = torch.from_numpy(grid.handle.get_mass()).cuda()
-    grid.ring.allreduce_sums(mass)
-    grid.handle.set_mass(mass.cpu().numpy())
-    grid.step(2)
-    ms = _timed(lambda: grid.step(steps), world)
+    return grid, mass
+
+
+def striped_mass_error(grid, mass):
+    """Largest relative deviation of the torus's per-channel masses from their targets (summed over the ranks)."""
     X = grid.read()
     s = torch.from_numpy(X.reshape(-1, 64).astype(np.float64).sum(0)).cuda()
     grid.ring.allreduce_sums(s)
-    err = float((s.cpu() - mass.cpu()[0]).abs().div(mass.cpu()[0].abs()).max())
+    return float((s.cpu() - mass.cpu()[0]).abs().div(mass.cpu()[0].abs()).max())
+
+
+def config4(args, rank, world, local):
+    edge, steps = 8192 // args.scale_down, 100
+    w = inputs.make_weight_sets(1, seed=42, bounded=True)
+    grid, mass = random_striped_grid(edge, args.dtype, rank, world, local, w)
+    grid.step(2)
+    ms = _timed(lambda: grid.step(steps), world)
+    split = grid.handle.step_ring_timed(10)
+    err = striped_mass_error(grid, mass)
     grid.close()
-    return {"config": 4, "workload": f"X[1,{edge},{edge},64] row stripes, {steps} steps, 3-row halo exchange + 64-value all-reduce per step",
+    return {"config": 4, "workload": f"X[1,{edge},{edge},64] row stripes, {steps} steps, 3-row halo exchange + 64-value all-reduce per step "
+                                     "(ring inside the C library: ncclSend/ncclRecv/ncclAllReduce on the stream)",
             "dtype": args.dtype, "n_gpus": world, "ms": ms, "cell_updates_per_s": edge * edge * steps / (ms * 1e-3),
-            "max_mass_error": err, "scaling": "strong"}
+            "ms_per_step_halo": split[0] / 10, "ms_per_step_kernels": split[1] / 10, "ms_per_step_allreduce": split[2] / 10,
+            "max_mass_error": err, "scaling": "strong", "weights": "mass-neutral variant of the specified draws"}
 
 
 def config5(args, rank, world, local):
     n_img, steps = 4096 // args.scale_down, 24
     per = n_img // world
     dt = capi.BF16 if args.dtype == "bf16" else capi.F32
-    w = inputs.make_weight_sets(1, seed=42)
     L, Wr, br = inputs.make_lift_readout(seed=42)
+    w = inputs.make_weight_sets(1, seed=42, bounded=True, mass_profile=L)
     img = inputs.make_images(per, 28, seed=42, first=rank * per)
     with capi.Handle(per, 32, 32, dtype=dt, device=local) as h:
         h.set_weights(w)
@@ -162,8 +177,8 @@ def config5(args, rank, world, local):
     return {"config": 5, "workload": f"{n_img} images 28x28 -> 32x32x64, {steps} steps, mean-pool + 64->10 read-out",
             "dtype": args.dtype, "n_gpus": world, "ms": ms, "cell_updates_per_s": n_img * 32 * 32 * steps / (ms * 1e-3),
             "logits_finite": bool(np.isfinite(logits).all()), "logit0": [float(v) for v in logits[0][:3]],
-            "note": "the lifted states (mass ~100 per channel) diverge under random weights: the fp64 CPU oracle of "
-                    "this workload is itself non-finite by step 16; throughput does not depend on the values"}
+            "weights": "mass-neutral variant of the specified draws for the lifted state's mass profile (the plain "
+                       "draws diverge within 16 steps, in the fp64 CPU oracle too)"}
 
 
 def main():

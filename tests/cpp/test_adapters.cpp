@@ -27,6 +27,16 @@ int main() {
         cudaMemcpy(d_in, x.data(), n * 4, cudaMemcpyHostToDevice);
         model->forward(d_in, d_mid);
         model->forward(d_mid, d_out);
+        {
+            // the documented protocol path: two chained forwards, then the component's fitness, with no launch() between
+            SlimeComponent chained(&pod, 1);
+            ComponentProtocol* c0 = &chained;
+            const float f0 = c0->compute_fitness();
+            if (!(f0 == f0) || !(std::fabs(f0 - model->effective_rank() * model->coherence()) < 1e-3f)) {
+                std::printf("forward -> compute_fitness: f=%g\n", f0);
+                return 1;
+            }
+        }
         std::vector<float> a(n), b(n);
         cudaMemcpy(a.data(), d_out, n * 4, cudaMemcpyDeviceToHost);
         // same two steps through KernelProtocol
@@ -38,7 +48,8 @@ int main() {
         double num = 0, den = 0;
         for (int i = 0; i < n; ++i) { num += (double)(a[i] - b[i]) * (a[i] - b[i]); den += (double)b[i] * b[i]; }
         if (!(std::sqrt(num / den) < 1e-5)) { std::printf("forward twice != two steps: %g\n", std::sqrt(num / den)); return 1; }
-        if (kp->memory_required() == 0 || !(kp->theoretical_occupancy() > 0.f)) { std::printf("kernel protocol\n"); return 1; }
+        const float occ = kp->theoretical_occupancy();    // fp32 path: 256-thread CTAs, at least one and at most eight per SM
+        if (kp->memory_required() == 0 || !(occ >= 256.f / 2048.f && occ <= 1.f)) { std::printf("kernel protocol: occupancy %g\n", occ); return 1; }
         SlimeComponent comp(&pod, 5);
         ComponentProtocol* cp = &comp;
         const float f = cp->compute_fitness();

@@ -39,7 +39,7 @@ def step_numpy(X, w, s, dt=0.1):
         U = sum(float(w.K[s, h, t]) * shift(P, dy, dx) for t, (dy, dx) in enumerate(TAPS))
         mu, sg = float(w.mu[s, h]), float(w.sigma[s, h])
         G = 2.0 * np.exp(-((U - mu) ** 2) / (2.0 * sg * sg)) - 1.0
-        A = G * I
+        A = np.clip(G * I, -80.0, 80.0)      # the step's domain limit on the activation (inactive in these fixtures)
         STATS.append(float((G > -0.9).mean()))
         # scatter: source s sends V(s) * softmax over its 9 targets n of A(n)
         nbrA = np.stack([shift(A, dy, dx) for dy, dx in TAPS])          # A at the 9 targets of each source

@@ -30,3 +30,20 @@ def load_golden(name):
 def channel_mass(X):
     X = np.asarray(X, np.float64)
     return X.reshape(X.shape[0], -1, X.shape[-1]).sum(axis=1)
+
+
+def bf16_round(a):
+    import torch
+    return torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(torch.bfloat16).float().numpy()
+
+
+def bf16_storage_floor(X0, w, steps, truth):
+    """Relative L2 distance from `truth` (the fp64 oracle after `steps` steps) of the same oracle when nothing but the
+    state is rounded to bf16 after every step: what bf16 storage of the state alone costs over that many steps,
+    whatever the arithmetic in between.  A bf16 kernel can not be expected to come closer than this."""
+    from oracle import ca_oracle
+    X = bf16_round(X0)
+    mass = ca_oracle.channel_mass(X)
+    for _ in range(steps):
+        X = bf16_round(ca_oracle.ca_steps(X, w, 1, literal=False, mass=mass))
+    return rel_l2(X, truth)

@@ -18,7 +18,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _stripe_worker(rank, world, port, H, W, steps, dtype, out_path):
+def _stripe_worker(rank, world, port, H, W, steps, dtype, out_path, library_ring):
     import torch
     import torch.distributed as dist
     from slime_b200 import capi, sharding
@@ -28,9 +28,11 @@ def _stripe_worker(rank, world, port, H, W, steps, dtype, out_path):
     try:
         X0 = inputs.make_state(1, H, W, seed=8, scale=0.45 * H * W)
         w = inputs.make_weight_sets(1, seed=8)
-        grid = sharding.StripedGrid(H, W, w, dtype=dtype, device=rank)
+        grid = sharding.StripedGrid(H, W, w, dtype=dtype, device=rank, library_ring=library_ring)
         grid.load(X0[:, grid.first_row:grid.first_row + grid.n_rows])
         grid.step(steps)
+        if library_ring:
+            grid.handle.ring_wait(60000)      # the bounded host wait of the library's ring
         np.save(out_path % rank, grid.read())
         grid.close()
         dist.barrier()
@@ -38,8 +40,11 @@ def _stripe_worker(rank, world, port, H, W, steps, dtype, out_path):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("library_ring", [True, False], ids=["library_ring", "python_ring"])
 @pytest.mark.parametrize("dtype_name", ["f32", "bf16"])
-def test_stripes_over_nccl_match_one_gpu(tmp_path, dtype_name):
+def test_stripes_over_nccl_match_one_gpu(tmp_path, dtype_name, library_ring):
+    """Two row stripes on two GPUs against one GPU holding the whole torus: through the ring inside the C library
+    (slime_ca_step_ring: ncclSend / ncclRecv / ncclAllReduce on the stream) and through the Python ring."""
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
@@ -54,7 +59,7 @@ def test_stripes_over_nccl_match_one_gpu(tmp_path, dtype_name):
         ref = h.get_state()
     port = _free_port()
     out = str(tmp_path / "stripe_%d.npy")
-    mp.spawn(_stripe_worker, args=(world, port, H, W, steps, dtype, out), nprocs=world, join=True)
+    mp.spawn(_stripe_worker, args=(world, port, H, W, steps, dtype, out, library_ring), nprocs=world, join=True)
     got = np.concatenate([np.load(out % r) for r in range(world)], axis=1)
     assert rel_l2(got, ref) < (1e-6 if dtype_name == "f32" else 2e-3)
 

@@ -125,3 +125,65 @@ def test_generators_are_counter_based():
     np.testing.assert_allclose(w.K.sum(axis=-1), 1.0, rtol=1e-6)
     assert (w.mu >= 0.1).all() and (w.mu <= 0.3).all() and (w.sigma >= 0.01).all() and (w.sigma <= 0.05).all()
     np.testing.assert_allclose(channel_mass(a), 1.0, rtol=1e-5)
+
+
+def test_specified_generators_grow_by_a_fixed_factor_per_step():
+    """With the generators as specified (unit mass, Wo ~ N(0, 1/512)) the per-channel sums move by about +-0.1 per
+    step, the renormalisation scales the channel with the most negative drift by about 1.38 every step, and the
+    state's zero-mean part grows by that factor: max|X| 1.2e-2 at step 16, 2.0 at 32, 380 at 48.  The clamp on the
+    activation keeps the closed form finite beyond that; without it exp(A) overflows between steps 48 and 56."""
+    X0 = inputs.make_state(1, 128, 128, seed=42)
+    w = inputs.make_weight_sets(1, seed=42)
+    m = ca_oracle.channel_mass(X0)
+    X, peak = X0, {}
+    for k in range(1, 9):
+        X = ca_oracle.ca_steps(X, w, 8, literal=False, mass=m)
+        peak[8 * k] = float(np.abs(X).max()) if np.isfinite(X).all() else float("nan")
+    assert peak[16] == pytest.approx(1.18e-2, rel=0.05) and peak[32] == pytest.approx(2.05, rel=0.05)
+    assert peak[48] == pytest.approx(379.0, rel=0.05)
+    for k in (16, 24, 32, 40, 48):
+        assert 1.33 < (peak[k] / peak[k - 8]) ** (1 / 8) < 1.43
+    assert np.isfinite(peak[64])                      # the clamp holds the closed form together
+    old = ca_oracle.set_activation_clamp(1e30)
+    try:
+        X = ca_oracle.ca_steps(X0, w, 48, literal=False, mass=m)
+        assert np.isfinite(X).all()
+        X = ca_oracle.ca_steps(X, w, 8, literal=False, mass=m)
+        assert not np.isfinite(X).all()               # unclamped: overflow between steps 48 and 56
+    finally:
+        ca_oracle.set_activation_clamp(old)
+
+
+def test_mass_neutral_weights_keep_long_trajectories_finite():
+    """The mass-neutral variant of the same draws (inputs.mass_neutral) leaves the channel sums where they are, so
+    the renormalisation scale stays at 1 and 100 steps grow the state by a few hundred, not by 1e14."""
+    X0 = inputs.make_state(1, 48, 48, seed=42)
+    w = inputs.make_weight_sets(1, seed=42, bounded=True)
+    plain = inputs.make_weight_sets(1, seed=42)
+    for a, b in zip(w.arrays(), plain.arrays()):
+        if a is not w.Wo:
+            np.testing.assert_array_equal(a, b)
+    drift = np.einsum("hcd,hdk->ck", plain.Wv[0].astype(np.float64), w.Wo[0].astype(np.float64).reshape(8, 64, 64)).sum(0)
+    assert np.abs(drift).max() < 1e-6                 # unit masses no longer move the channel sums
+    X1 = ca_oracle.ca_steps(X0, w, 1, literal=False, renorm=False)
+    np.testing.assert_allclose(channel_mass(X1), channel_mass(X0), rtol=2e-6)
+    X = ca_oracle.ca_steps(X0, w, 100, literal=False)
+    assert np.isfinite(X).all() and np.abs(X).max() < 2000 * np.abs(X0).max()
+
+
+def test_activation_clamp_acts_only_beyond_80():
+    X0 = inputs.make_state(1, 8, 8, seed=3, scale=30.0)
+    w = inputs.make_weight_sets(1, seed=3)
+    a = ca_oracle.ca_steps(X0, w, 2, literal=True)
+    old = ca_oracle.set_activation_clamp(1e30)
+    try:
+        b = ca_oracle.ca_steps(X0, w, 2, literal=True)
+        assert np.array_equal(a, b)                   # |G I| stays far below 80 here
+        w.Wi *= 4000.0                                # interaction large enough for |G I| > 80
+        c = ca_oracle.ca_steps(X0, w, 1, literal=True)
+    finally:
+        ca_oracle.set_activation_clamp(old)
+    d = ca_oracle.ca_steps(X0, w, 1, literal=True)
+    e = ca_oracle.ca_steps(X0, w, 1, literal=False)
+    assert rel_l2(d, c) > 1e-6                        # the clamp changed the function there
+    assert rel_l2(e, d) < 1e-7                        # and both forms of the oracle agree on the clamped one

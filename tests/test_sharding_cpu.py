@@ -89,3 +89,39 @@ def test_ring_halo_exchange_and_allreduce_over_gloo(world):
         p.join(timeout=120)
         assert p.exitcode == 0
     assert list(out) == [1] * world
+
+
+def _timeout_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    ring = sharding.StripeRing(timeout_s=1.0)
+    st = torch.zeros(1, 4 + 6, 3, 64)
+    if rank == 0:
+        # rank 1 never takes part in this exchange: the wait must end with RingTimeout, not block
+        try:
+            ring.exchange_halos(st, 4)
+            out[0] = 0
+        except sharding.RingTimeout as e:
+            out[0] = 1 if "halo rows" in str(e) else 0
+    else:
+        import time
+        t0 = time.monotonic()
+        while out[0] < 0 and time.monotonic() - t0 < 30:      # stay connected, but silent, until rank 0 has given up
+            time.sleep(0.05)
+        out[1] = 1
+    # the transfers rank 0 posted can never complete: leave without the collective teardown
+    os._exit(0)
+
+
+def test_ring_wait_is_bounded_when_a_neighbour_never_sends():
+    port = _free_port()
+    ctx = mp.get_context("spawn")
+    out = ctx.Array("i", [-1, -1])
+    procs = [ctx.Process(target=_timeout_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert list(out) == [1, 1]
