@@ -32,9 +32,10 @@ k_channel_partials(const T* __restrict__ X, float* __restrict__ partial, Geom g)
     if (sub == 0) partial[((size_t)b * gridDim.x + blockIdx.x) * NC + c] = (red[0][c] + red[1][c]) + (red[2][c] + red[3][c]);
 }
 
-// Stage 1 of the cross-tile reduction: segment s of grid b sums its share of the partials in fp64.
+// Stage 1 of the cross-tile reduction: segment s of grid b sums its share of the partials in fp64.  lo_offset != 0:
+// every partial is a float pair, the remainder lo_offset floats after the value (the fp32 step kernel's tile sums).
 __global__ void __launch_bounds__(256)
-k_reduce_partials(const float* __restrict__ partial, int n_partials, double* __restrict__ seg_sums) {
+k_reduce_partials(const float* __restrict__ partial, int n_partials, double* __restrict__ seg_sums, size_t lo_offset = 0) {
     __shared__ double red[4][64];
     const int b = blockIdx.y, c = threadIdx.x & 63, sub = threadIdx.x >> 6;
     const int nseg = gridDim.x;
@@ -45,7 +46,11 @@ k_reduce_partials(const float* __restrict__ partial, int n_partials, double* __r
     const int seg_hi = min((blockIdx.x + 1) * per_seg, n_partials);
     if (hi > seg_hi) hi = seg_hi;
     double s = 0.0;
-    for (int t = lo; t < hi; ++t) s += (double)partial[((size_t)b * n_partials + t) * NC + c];
+    for (int t = lo; t < hi; ++t) {
+        const size_t o = ((size_t)b * n_partials + t) * NC + c;
+        s += (double)partial[o];
+        if (lo_offset) s += (double)partial[o + lo_offset];
+    }
     red[sub][c] = s;
     __syncthreads();
     if (sub == 0) seg_sums[((size_t)b * nseg + blockIdx.x) * NC + c] = (red[0][c] + red[1][c]) + (red[2][c] + red[3][c]);

@@ -5,13 +5,11 @@
 //   k1_bf16  per 8x16-cell tile (128 cells = UMMA M): state halo tile -> per head the 3x3-convolved input as a
 //            swizzled K-major A operand; U = conv_h(X) Wp_h (N=64) and I|V = X [Wi_h|Wv_h] (N=128) into 192
 //            TMEM columns; epilogue: growth bell, E = exp(G*I), write E and V (bf16, per-head planes).
-//   k2_bf16  persistent, warp-specialised, one CTA per SM.  A producer warp streams (tile, head) items - the E
-//            tile with a 2-cell halo, the V tile with a 1-cell halo and the head's Wo slice - through a 3-stage
-//            TMA ring; two groups of 9 compute warps take alternate heads: separable box sums marching down
-//            columns in packed fp32 (R = V / box3(E) in place, V' = E * box3(R)), V' written as a swizzled A
-//            operand; an MMA warp issues Y += V'_h Wo_h (N=64) into a double-buffered TMEM accumulator in head
-//            order; the epilogue X+ = scale*X + dt*Y (bf16, in place) and the tile's channel sums run one tile
-//            behind.
+//   k2_bf16  persistent, warp-specialised, one CTA per SM: macro tiles of 32 columns, marched four rows at a time
+//            per head with the box sums' vertical running sums carried in registers; R = V / box3(E) and
+//            V' = E * box3(R) on two sets of warps one block apart, V' written as a swizzled A operand; an MMA warp
+//            issues Y += V'_h Wo_h (N=64) into one TMEM accumulator per 4 x 32-cell tile in head order; the epilogue
+//            X+ = scale*X + dt*Y (bf16, in place) and the tiles' channel sums run one macro tile behind.
 //
 // E/V planes are [B][8][H+4][W+4][64] with a 2-cell apron all around: k1 writes every cell it computes to its
 // own position and to every apron position that wraps onto it, so k2 never wraps or clamps and each of its
@@ -45,10 +43,11 @@ struct Bf16Plan {
     int tiles_x = 1, k1_tiles = 1, k2_tiles = 1, k1_grid = 1, k2_grid = 1;
     CUtensorMap map_w1;   // [sets*8*192][64] bf16, box 64 x 192, 128B swizzle
     CUtensorMap map_wo;   // [sets*8*64][64]  bf16, box 64 x 64,  128B swizzle
-    CUtensorMap map_e;    // E planes [B*8][H+4][W+4][64], box 64 x 20 x 12 x 1
-    CUtensorMap map_v;    // V planes, box 64 x 18 x 10 x 1
+    CUtensorMap map_e;    // E planes [B*8][H+4][W+4][64], box 64 x 36 x 4 x 1 (a block of k2)
+    CUtensorMap map_v;    // V planes, box 64 x 34 x 4 x 1
     K1StoreMaps st;       // store maps of k1 (whole tile, last two columns, last two rows, their corner)
     bool k1_aligned = false;
+    int strips = 1, mt_per_grid = 1, nbmax = 8;    // k2: 32-column strips, macro tiles per grid, blocks per macro tile
 };
 
 // ---- shared-memory maps (byte offsets from a 1024-aligned base) -------------------------------------------
@@ -69,23 +68,6 @@ constexpr uint32_t TMEM_COLS = 512;   // two accumulator buffers of 192 columns
 constexpr int THREADS = 576;
 static_assert(SMEM <= 227 * 1024, "k1 shared memory");
 }  // namespace k1b
-namespace k2b {
-constexpr int STAGES = 3;
-constexpr int WO_OFF = 0, E_OFF = 8192, E_BYTES = 12 * 20 * 128, V_OFF = E_OFF + E_BYTES, V_BYTES = 10 * 18 * 128;
-constexpr uint32_t STAGE_TX = 8192 + E_BYTES + V_BYTES;                 // 61952 bytes land per item
-constexpr int STAGE_BYTES = 62464;                                      // rounded up to a multiple of 1024
-constexpr int A_VP = STAGES * STAGE_BYTES;                              // two 16 KB operand tiles, one per group
-constexpr int RED = A_VP + 2 * 16384;                                   // [2 groups][4 quads][64] fp32
-constexpr int BARS = RED + 2 * 4 * 64 * 4;
-constexpr int TMEM_PTR = BARS + 20 * 8;
-constexpr int BYTES = TMEM_PTR + 16;
-constexpr int SMEM = BYTES + 1024;
-constexpr uint32_t TMEM_COLS = 128;                                     // two 64-column accumulators
-constexpr int GROUP = 288;                                              // compute threads per group (9 warps)
-constexpr int THREADS = 2 * GROUP + 64;                                 // + TMA warp + MMA warp
-static_assert(STAGE_TX <= STAGE_BYTES && STAGE_BYTES % 1024 == 0, "stage layout");
-static_assert(SMEM <= 227 * 1024, "k2 shared memory");
-}  // namespace k2b
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
@@ -496,15 +478,28 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
 
 // Epilogue of one finished tile, run by 8 warps (256 threads) of one compute group: X+ = scale*X + dt*Y in
 // place, and the tile's per-channel sums of the stored (rounded) values -> partial[tile][64].
-__device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr, __nv_bfloat16* __restrict__ X,
-                                            const float* __restrict__ scale, float* __restrict__ partial,
-                                            float* red, int bar_id, int gt, int cta_warp, const Geom& g) {
+// Epilogue of a finished tile.  WSHIFT: the tile is (128 >> WSHIFT) rows of (1 << WSHIFT) cells, cell m of the tile in
+// TMEM lane m.
+// This thread's cell of a finished tile: where its 32 channels of X live (null when the cell lies outside the grid)
+template <int WSHIFT>
+__device__ __forceinline__ __nv_bfloat16* k2_epilogue_cell(const CaTile& t, __nv_bfloat16* __restrict__ X, int gt,
+                                                           int cta_warp, const Geom& g) {
     const int lane = gt & 31, quad = cta_warp & 3, half = (gt >> 5) >> 2;
     const int m = quad * 32 + lane;
-    const int r = t.ty0 + (m >> 4), x = t.tx0 + (m & 15);
-    const bool valid = r < g.H && x < g.W;
+    const int r = t.ty0 + (m >> WSHIFT), x = t.tx0 + (m & ((1 << WSHIFT) - 1));
+    if (!(r < g.H && x < g.W)) return nullptr;
     const size_t xplane = (size_t)g.state_rows() * g.W * NC;
-    __nv_bfloat16* px = X + (size_t)t.b * xplane + ((size_t)g.xrow(valid ? r : 0) * g.W + (valid ? x : 0)) * NC;
+    return X + (size_t)t.b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC + half * 32;
+}
+// xin: the thread's 32 channels of X as loaded by the caller before it waited for the accumulator (4 x 16 bytes)
+template <int WSHIFT>
+__device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr, __nv_bfloat16* __restrict__ pcell,
+                                            const uint4 (&xin)[4], const float* __restrict__ scale,
+                                            float* __restrict__ partial, float* red, int bar_id, int gt, int cta_warp,
+                                            const Geom& g) {
+    const int lane = gt & 31, quad = cta_warp & 3, half = (gt >> 5) >> 2;
+    const bool valid = pcell != nullptr;
+    __nv_bfloat16* px = pcell - half * 32;
     const float* sc = scale + t.b * NC;
 #pragma unroll
     for (int sub = 0; sub < 2; ++sub) {
@@ -515,8 +510,8 @@ __device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr,
         float xo[16];
         if (valid) {
             float f0[8], f1[8], sv[16];
-            unpack8(*reinterpret_cast<const uint4*>(px + c0), f0);
-            unpack8(*reinterpret_cast<const uint4*>(px + c0 + 8), f1);
+            unpack8(xin[2 * sub], f0);
+            unpack8(xin[2 * sub + 1], f1);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const float4 s4 = __ldg(reinterpret_cast<const float4*>(sc + c0) + k);
@@ -561,198 +556,299 @@ __device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr,
     if (gt < NC) partial[(size_t)t.index * NC + gt] = (red[gt] + red[64 + gt]) + (red[128 + gt] + red[192 + gt]);
 }
 
-__global__ void __launch_bounds__(k2b::THREADS, 1)
+// =============================================================================================================
+// k2.  The grid is cut into macro tiles of 32 columns x 32 rows; a macro tile is eight 4 x 32-cell tiles (UMMA
+// M = 128) stacked in y, one 64-column TMEM accumulator each (8 x 64 = all 512 columns; launches with too few macro
+// tiles to fill the GPU use 4, 2 or 1 tiles per macro tile instead).  For one head
+// after the other the kernel marches down the macro tile four rows at a time, carrying the vertical running sums of
+// both box sums in registers from block to block, so every E and V row of the strip is loaded and summed once per
+// head (square tiles with a 2-cell ring all round re-read 1.9x the E rows and 1.4x the V rows at 8 x 16 cells).  A
+// block is 4 rows of the strip: E rows with a 2-column ring (36 cells), V rows with a 1-column ring (34 cells), 35 KB,
+// in a 5-stage ring.  Block -1 of a march only primes the registers (E rows -2..1, R rows -1..0 of the macro tile).
+// The two box sums run on different warps, one block apart, with no barrier inside either set:
+//   warps 0-7,19 A: R = V / box3(E) in place in the stage, one thread per (column of the 34, 8 dims); hands the block
+//                to B through a named barrier it only arrives on
+//   warps 8-15   B: V' = E * box3(R) -> one of two swizzled A operand tiles (every thread arrives on the operand's
+//                mbarrier), then releases the stage
+//   warp 16      TMA producer: per (macro tile, head) the head's Wo slice (double-buffered), per block E and V
+//   warp 17      UMMA issuer: Y[tile] += V'_h Wo_h, heads in order          (warp 18 has no role)
+// so that each of the SM's four schedulers (warp index mod 4) carries two A warps and two B warps, the half-filled
+// ninth A warp sits alone on the fourth, and the two single-thread roles on the first two.
+// The epilogue of a macro tile (X+ = scale X + dt Y, channel sums) is interleaved into the first head of the next one:
+// A's first eight warps drain the even accumulators, B the odd ones, each just before its own block of that tile.
+// Every cell's arithmetic is the same sequence of operations wherever the cell sits in a tile or a block, so shifting a
+// torus shifts the result bit for bit.
+// Eight fp32 values (the 8 dims a thread owns) as four packed pairs, and the few operations the box sums need on them
+// (add / mul.f32x2; a plain-fp32 version of the same operations measured 4 % slower).
+struct V8 { ptx::f2 v[4]; };
+__device__ __forceinline__ V8 v8_zero() { V8 r; for (int i = 0; i < 4; ++i) r.v[i] = ptx::make_f2(0.f, 0.f); return r; }
+__device__ __forceinline__ V8 v8_sum3(const uint4& a, const uint4& b, const uint4& c) {
+    V8 r;
+    r.v[0] = ptx::sum3_bf16x2(a.x, b.x, c.x); r.v[1] = ptx::sum3_bf16x2(a.y, b.y, c.y);
+    r.v[2] = ptx::sum3_bf16x2(a.z, b.z, c.z); r.v[3] = ptx::sum3_bf16x2(a.w, b.w, c.w);
+    return r;
+}
+__device__ __forceinline__ V8 v8_add(const V8& a, const V8& b) { V8 r; for (int i = 0; i < 4; ++i) r.v[i] = ptx::add2(a.v[i], b.v[i]); return r; }
+__device__ __forceinline__ V8 v8_mul(const V8& a, const V8& b) { V8 r; for (int i = 0; i < 4; ++i) r.v[i] = ptx::mul2(a.v[i], b.v[i]); return r; }
+__device__ __forceinline__ V8 v8_rcp(const V8& a) {
+    V8 r;
+    for (int i = 0; i < 4; ++i) { float z0, z1; ptx::split_f2(a.v[i], z0, z1); r.v[i] = ptx::make_f2(ptx::rcp(z0), ptx::rcp(z1)); }
+    return r;
+}
+__device__ __forceinline__ V8 v8_unpack(const uint4& w) { V8 r; unpack8p(w, r.v); return r; }
+__device__ __forceinline__ uint4 v8_pack(const V8& a) { return pack8p(a.v); }
+
+namespace k2m {
+constexpr int SW = 32, BR = 4, NB = 8;                  // strip width, rows per block, blocks per macro tile
+constexpr int MTH = BR * NB;                            // macro tile height
+constexpr int EW = SW + 4, VW = SW + 2;                 // cells per E / V row of a block
+constexpr int E_BYTES = BR * EW * 128, V_BYTES = BR * VW * 128;
+constexpr int STAGE_BYTES = E_BYTES + V_BYTES;          // 35 840
+constexpr uint32_t STAGE_TX = STAGE_BYTES;
+constexpr int NSTAGE = 5;
+constexpr int STG = 0;
+constexpr int A_VP = STG + NSTAGE * STAGE_BYTES;        // two 16 KB operand tiles
+constexpr int WO = A_VP + 2 * 16384;                    // two 8 KB Wo slices
+constexpr int RED = WO + 2 * 8192;                      // [A, B][4 quads][64] fp32
+constexpr int BARS = RED + 2 * 4 * 64 * 4;
+constexpr int N_BARS = NSTAGE + NSTAGE + 2 + 2 + 2 + 2 + NB + NB;
+constexpr int TMEM_PTR = BARS + N_BARS * 8;
+constexpr int BYTES = TMEM_PTR + 16;
+constexpr int SMEM = BYTES + 1024;
+constexpr uint32_t TMEM_COLS = 512;
+constexpr int A_THREADS = 288, B_THREADS = 256;
+constexpr int THREADS = 640;                            // 20 warps, see the kernel for who does what
+constexpr int HANDOFF = A_THREADS + B_THREADS;          // parties of the named barrier that hands a block from A to B
+static_assert(STAGE_BYTES % 1024 == 0 && A_VP % 1024 == 0 && WO % 1024 == 0, "operand tiles must be 1024-byte aligned");
+static_assert(SMEM <= 227 * 1024, "k2 (marching) shared memory");
+}  // namespace k2m
+
+// Macro tile `idx` of the launch: grid, origin, number of 4-row blocks that hold own rows.
+struct MacroTile {
+    int b, mx0, my0, nb, tile0;     // tile0: index of its first 4 x 32 tile among the grid's partial sums
+};
+// nbmax: blocks per full macro tile of this launch (8, 4, 2 or 1)
+__device__ __forceinline__ MacroTile macro_tile(int idx, int per_grid, int strips, int H, int nbmax) {
+    MacroTile m;
+    m.b = idx / per_grid;
+    const int r = idx - m.b * per_grid, my = r / strips, sx = r - my * strips;
+    m.mx0 = sx * k2m::SW;
+    m.my0 = my * nbmax * k2m::BR;
+    const int left = (H - m.my0 + k2m::BR - 1) / k2m::BR;
+    m.nb = left < nbmax ? left : nbmax;
+    m.tile0 = (my * nbmax) * strips + sx;         // tile (block row y4, strip sx) has index y4 * strips + sx
+    return m;
+}
+
+__global__ void __launch_bounds__(k2m::THREADS, 1)
 k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUtensorMap map_e,
-        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ X, const float* __restrict__ scale,
-        float* __restrict__ partial, __nv_bfloat16* __restrict__ vprime, int* __restrict__ status, int n_tiles,
-        int tiles_per_grid, Geom g) {
+              const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ X, const float* __restrict__ scale,
+              float* __restrict__ partial, __nv_bfloat16* __restrict__ vprime, int* __restrict__ status, int n_mt,
+              int mt_per_grid, int strips, int tiles_per_grid, int nbmax, Geom g) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* sm = align1024(smem_raw);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + k2b::BARS);
-    // Every barrier has exactly one waiting party that observes each of its phases in turn (a parity wait can
-    // not tell a phase from the one two earlier).  Items alternate between the two compute groups and between
-    // three stages, so "TMA landed" is kept per (group, stage): item i uses full[(i & 1) * 3 + i % 3], phase i / 6.
-    uint64_t* full = bars;              // [2][3] TMA landed in stage s for group g
-    uint64_t* empty = bars + 6;         // [3]  the UMMA of the item in stage s is done (Wo read; E/V long since)
-    uint64_t* vp_full = bars + 9;       // [2]  group g's operand tile is written
-    uint64_t* vp_empty = bars + 11;     // [2]  the UMMA reading group g's operand tile is done
-    uint64_t* acc_full = bars + 13;     // [2]  all 8 heads of a tile are accumulated
-    uint64_t* acc_empty = bars + 15;    // [2]  the epilogue has drained the accumulator
-    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(sm + k2b::TMEM_PTR);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sm + k2m::BARS);
+    uint64_t* full = bars;                           // [5] block landed                              (waits: A)
+    uint64_t* empty = full + k2m::NSTAGE;            // [5] B is done with the stage (256 arrivals)   (waits: TMA producer)
+    uint64_t* vp_full = empty + k2m::NSTAGE;         // [2] operand tile written (256 arrivals)       (waits: UMMA issuer)
+    uint64_t* vp_empty = vp_full + 2;                // [2] the UMMAs reading it are done             (waits: B)
+    uint64_t* wo_full = vp_empty + 2;                // [2] Wo slice landed                           (waits: UMMA issuer)
+    uint64_t* wo_empty = wo_full + 2;                // [2] the head that used it is issued and done  (waits: TMA producer)
+    uint64_t* acc_full = wo_empty + 2;               // [8] all 8 heads of the tile accumulated       (waits: who drains it)
+    uint64_t* acc_empty = acc_full + k2m::NB;        // [8] drained (256 arrivals)                    (waits: UMMA issuer)
+    uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(sm + k2m::TMEM_PTR);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) {
-        for (int i = 0; i < 6; ++i) ptx::mbar_init(&full[i], 1);
-        for (int i = 0; i < 3; ++i) ptx::mbar_init(&empty[i], 1);
+        // (every thread of a set arrives by itself: one arrival per warp behind a __syncwarp measured 3 % slower)
+        for (int i = 0; i < k2m::NSTAGE; ++i) { ptx::mbar_init(&full[i], 1); ptx::mbar_init(&empty[i], k2m::B_THREADS); }
         for (int i = 0; i < 2; ++i) {
-            ptx::mbar_init(&vp_full[i], 1); ptx::mbar_init(&vp_empty[i], 1);
-            ptx::mbar_init(&acc_full[i], 1); ptx::mbar_init(&acc_empty[i], 256);
+            ptx::mbar_init(&vp_full[i], k2m::B_THREADS); ptx::mbar_init(&vp_empty[i], 1);
+            ptx::mbar_init(&wo_full[i], 1); ptx::mbar_init(&wo_empty[i], 1);
         }
+        for (int i = 0; i < k2m::NB; ++i) { ptx::mbar_init(&acc_full[i], 1); ptx::mbar_init(&acc_empty[i], 256); }
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&map_wo); ptx::prefetch_tmap(&map_e); ptx::prefetch_tmap(&map_v);
     }
-    if (warp == 0) ptx::tmem_alloc(tmem_ptr, k2b::TMEM_COLS);
+    if (warp == 0) ptx::tmem_alloc(tmem_ptr, k2m::TMEM_COLS);
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem = *tmem_ptr;
-    const int my_tiles = n_tiles > (int)blockIdx.x ? (n_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int my_mt = n_mt > (int)blockIdx.x ? (n_mt - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
-    if (warp == 18) {
+    if (warp == 16) {
         // ================= TMA producer ===================================================================
         if (lane == 0) {
-            for (int k = 0; k < my_tiles; ++k) {
-                const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, 0);
-                const int set = t.b / g.per_set;
-                for (int h = 0; h < NH; ++h) {
-                    const int i = k * NH + h, s = i % 3, u = i / 3;
-                    ptx::mbar_wait(&empty[s], (u & 1) ^ 1, status, 210);
-                    uint8_t* st = sm + s * k2b::STAGE_BYTES;
-                    uint64_t* fb = &full[(h & 1) * 3 + s];
-                    ptx::mbar_expect_tx(fb, k2b::STAGE_TX);
-                    ptx::tma_load_2d(st + k2b::WO_OFF, &map_wo, 0, (set * NH + h) * 64, fb);
-                    ptx::tma_load_4d(st + k2b::E_OFF, &map_e, 0, t.tx0, t.ty0, t.b * NH + h, fb);
-                    ptx::tma_load_4d(st + k2b::V_OFF, &map_v, 0, t.tx0 + 1, t.ty0 + 1, t.b * NH + h, fb);
-                    // pull the item three ahead into L2 while this one streams into shared memory
-                    const int j = i + 3, kj = j / NH, hj = j % NH;
-                    if (kj < my_tiles) {
-                        const CaTile tj = ca_tile(blockIdx.x + kj * gridDim.x, tiles_per_grid, g.tiles_x, 0);
-                        ptx::tma_prefetch_4d(&map_e, 0, tj.tx0, tj.ty0, tj.b * NH + hj);
-                        ptx::tma_prefetch_4d(&map_v, 0, tj.tx0 + 1, tj.ty0 + 1, tj.b * NH + hj);
+            uint32_t it = 0, wit = 0;       // blocks and heads so far
+            for (int k = 0; k < my_mt; ++k) {
+                const MacroTile m = macro_tile(blockIdx.x + k * gridDim.x, mt_per_grid, strips, g.H, nbmax);
+                const int set = m.b / g.per_set;
+                for (int h = 0; h < NH; ++h, ++wit) {
+                    const int wb = wit & 1, plane = m.b * NH + h;
+                    ptx::mbar_wait(&wo_empty[wb], ((wit >> 1) & 1) ^ 1, status, 210);
+                    ptx::mbar_expect_tx(&wo_full[wb], 8192);
+                    ptx::tma_load_2d(sm + k2m::WO + wb * 8192, &map_wo, 0, (set * NH + h) * 64, &wo_full[wb]);
+                    for (int b = -1; b < m.nb; ++b, ++it) {
+                        const int s = it % k2m::NSTAGE;
+                        uint8_t* st = sm + k2m::STG + s * k2m::STAGE_BYTES;
+                        ptx::mbar_wait(&empty[s], ((it / k2m::NSTAGE) & 1) ^ 1, status, 211);
+                        ptx::mbar_expect_tx(&full[s], k2m::STAGE_TX);
+                        // E rows 4b+2 .. 4b+5 and V rows 4b+1 .. 4b+4 of the macro tile; plane coordinates carry the
+                        // 2-cell apron (block -1 of the first macro-tile row starts V one row above the plane: rows
+                        // outside the tensor read as zero and only feed values nobody uses)
+                        ptx::tma_load_4d(st, &map_e, 0, m.mx0, m.my0 + 4 * b + 4, plane, &full[s]);
+                        ptx::tma_load_4d(st + k2m::E_BYTES, &map_v, 0, m.mx0 + 1, m.my0 + 4 * b + 3, plane, &full[s]);
                     }
                 }
             }
         }
-    } else if (warp == 19) {
+    } else if (warp == 17) {
         // ================= UMMA issuer ====================================================================
         if (lane == 0) {
             const uint32_t idesc = ptx::umma_idesc_bf16(128, 64);
-            for (int k = 0; k < my_tiles; ++k) {
-                const int ab = k & 1, w = k >> 1;
-                for (int h = 0; h < NH; ++h) {
-                    const int i = k * NH + h, s = i % 3, grp = h & 1, v = i >> 1;
-                    if (h == 0) ptx::mbar_wait(&acc_empty[ab], (w & 1) ^ 1, status, 220);
-                    ptx::mbar_wait(&full[grp * 3 + s], (i / 6) & 1, status, 221);
-                    ptx::mbar_wait(&vp_full[grp], v & 1, status, 222);
-                    ptx::tc_fence_after();
-                    const uint64_t da = ptx::umma_desc_sw128(ptx::smem_u32(sm + k2b::A_VP + grp * 16384));
-                    const uint64_t dw = ptx::umma_desc_sw128(ptx::smem_u32(sm + s * k2b::STAGE_BYTES + k2b::WO_OFF));
+            uint32_t v = 0, wit = 0, acc_par = 0;     // operand tiles used, heads, use parity of each accumulator
+            for (int k = 0; k < my_mt; ++k) {
+                const MacroTile m = macro_tile(blockIdx.x + k * gridDim.x, mt_per_grid, strips, g.H, nbmax);
+                for (int h = 0; h < NH; ++h, ++wit) {
+                    const int wb = wit & 1;
+                    for (int b = 0; b < m.nb; ++b, ++v) {
+                        const int buf = v & 1;
+                        if (h == 0) ptx::mbar_wait(&acc_empty[b], ((acc_par >> b) & 1) ^ 1, status, 220);
+                        if (b == 0) ptx::mbar_wait(&wo_full[wb], (wit >> 1) & 1, status, 221);
+                        ptx::mbar_wait(&vp_full[buf], (v >> 1) & 1, status, 222);
+                        ptx::tc_fence_after();
+                        const uint64_t da = ptx::umma_desc_sw128(ptx::smem_u32(sm + k2m::A_VP + buf * 16384));
+                        const uint64_t dw = ptx::umma_desc_sw128(ptx::smem_u32(sm + k2m::WO + wb * 8192));
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        ptx::umma_bf16(tmem + ab * 64, da + 2 * kk, dw + 2 * kk, idesc, h > 0 || kk > 0);
-                    ptx::umma_commit(&empty[s]);
-                    ptx::umma_commit(&vp_empty[grp]);
-                    if (h == NH - 1) ptx::umma_commit(&acc_full[ab]);
-                }
-            }
-        }
-    } else {
-        // ================= compute groups: group 0 = warps 0..8 takes even heads, group 1 = warps 9..17 odd ====
-        const int grp = warp >= 9 ? 1 : 0;
-        const int gt = tid - grp * k2b::GROUP;          // 0..287 inside the group
-        const int bar_main = 1 + grp, bar_ep = 3 + grp;
-        uint8_t* a_vp = sm + k2b::A_VP + grp * 16384;
-        float* red = reinterpret_cast<float*>(sm + k2b::RED) + grp * 256;
-        const size_t vplane = (size_t)g.H * g.W * HD;
-        CaTile prev;
-        prev.index = -1;
-        for (int k = 0; k < my_tiles; ++k) {
-            const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, 0);
-            for (int h = grp; h < NH; h += 2) {
-                const int i = k * NH + h, s = i % 3, v = i >> 1;
-                uint8_t* es = sm + s * k2b::STAGE_BYTES + k2b::E_OFF;   // [12][20] cells x 128 B
-                uint8_t* vs = sm + s * k2b::STAGE_BYTES + k2b::V_OFF;   // [10][18] cells x 128 B: V, then R in place
-                ptx::mbar_wait(&full[grp * 3 + s], (i / 6) & 1, status, 230);
-
-                // ---- R = V / box3(E) on the 10 x 18 ring-extended tile: 18 columns x 8 chunks x 2 row segments ----
-                {
-                    const int q = gt & 7, c = (gt >> 3) % 18, r0 = (gt / 144) * 5;
-                    ptx::f2 hp2[4], hp1[4];
-#pragma unroll
-                    for (int j = 0; j < 7; ++j) {
-                        const uint8_t* row = es + ((r0 + j) * 20 + c) * 128 + q * 16;
-                        const uint4 e0 = *reinterpret_cast<const uint4*>(row);
-                        const uint4 e1 = *reinterpret_cast<const uint4*>(row + 128);
-                        const uint4 e2 = *reinterpret_cast<const uint4*>(row + 256);
-                        ptx::f2 hs[4];
-                        hs[0] = ptx::sum3_bf16x2(e0.x, e1.x, e2.x); hs[1] = ptx::sum3_bf16x2(e0.y, e1.y, e2.y);
-                        hs[2] = ptx::sum3_bf16x2(e0.z, e1.z, e2.z); hs[3] = ptx::sum3_bf16x2(e0.w, e1.w, e2.w);
-                        if (j >= 2) {
-                            uint4* pv = reinterpret_cast<uint4*>(vs + ((r0 + j - 2) * 18 + c) * 128 + q * 16);
-                            ptx::f2 vv[4];
-                            unpack8p(*pv, vv);
-#pragma unroll
-                            for (int n = 0; n < 4; ++n) {
-                                float z0, z1;
-                                ptx::split_f2(ptx::add2(ptx::add2(hp2[n], hp1[n]), hs[n]), z0, z1);
-                                vv[n] = ptx::mul2(vv[n], ptx::make_f2(ptx::rcp(z0), ptx::rcp(z1)));
-                            }
-                            *pv = pack8p(vv);
-                        }
-#pragma unroll
-                        for (int n = 0; n < 4; ++n) { hp2[n] = hp1[n]; hp1[n] = hs[n]; }
+                        for (int kk = 0; kk < 4; ++kk)
+                            ptx::umma_bf16(tmem + b * 64, da + 2 * kk, dw + 2 * kk, idesc, h > 0 || kk > 0);
+                        ptx::umma_commit(&vp_empty[buf]);
+                        if (b == m.nb - 1) ptx::umma_commit(&wo_empty[wb]);
+                        if (h == NH - 1) ptx::umma_commit(&acc_full[b]);
                     }
                 }
-                ptx::bar_sync(bar_main, k2b::GROUP);
-                ptx::mbar_wait(&vp_empty[grp], (v & 1) ^ 1, status, 231);   // the UMMA two heads back is done with a_vp
-
-                // ---- V' = E * box3(R) on the 8 x 16 tile: 16 columns x 8 chunks x 2 row segments -> A operand ----
-                if (gt < 256) {
-                    const int q = gt & 7, c = (gt >> 3) & 15, r0 = (gt >> 7) * 4;
-                    ptx::f2 hp2[4], hp1[4];
-#pragma unroll
-                    for (int j = 0; j < 6; ++j) {
-                        const uint8_t* row = vs + ((r0 + j) * 18 + c) * 128 + q * 16;
-                        const uint4 a0 = *reinterpret_cast<const uint4*>(row);
-                        const uint4 a1 = *reinterpret_cast<const uint4*>(row + 128);
-                        const uint4 a2 = *reinterpret_cast<const uint4*>(row + 256);
-                        ptx::f2 hs[4];
-                        hs[0] = ptx::sum3_bf16x2(a0.x, a1.x, a2.x); hs[1] = ptx::sum3_bf16x2(a0.y, a1.y, a2.y);
-                        hs[2] = ptx::sum3_bf16x2(a0.z, a1.z, a2.z); hs[3] = ptx::sum3_bf16x2(a0.w, a1.w, a2.w);
-                        if (j >= 2) {
-                            const int orow = r0 + j - 2;
-                            ptx::f2 e[4];
-                            unpack8p(*reinterpret_cast<const uint4*>(es + ((orow + 2) * 20 + c + 2) * 128 + q * 16), e);
-#pragma unroll
-                            for (int n = 0; n < 4; ++n) e[n] = ptx::mul2(e[n], ptx::add2(ptx::add2(hp2[n], hp1[n]), hs[n]));
-                            const uint4 out = pack8p(e);
-                            *reinterpret_cast<uint4*>(a_vp + swz(orow * TBW + c, q)) = out;
-                            if (vprime != nullptr && t.ty0 + orow < g.H && t.tx0 + c < g.W)
-                                *reinterpret_cast<uint4*>(vprime + ((size_t)t.b * NH + h) * vplane +
-                                                          ((size_t)(t.ty0 + orow) * g.W + t.tx0 + c) * HD + q * 8) = out;
-                        }
-#pragma unroll
-                        for (int n = 0; n < 4; ++n) { hp2[n] = hp1[n]; hp1[n] = hs[n]; }
-                    }
-                }
-                ptx::fence_proxy_async();
-                ptx::bar_sync(bar_main, k2b::GROUP);
-                if (gt == 0) ptx::mbar_arrive(&vp_full[grp]);
-
-                // ---- epilogue of the previous tile, one tile behind, by the group of that tile's parity --------
-                if (h == 2 + grp && prev.index >= 0 && ((k - 1) & 1) == grp && gt < 256) {
-                    const int pk = k - 1, ab = pk & 1, w = pk >> 1;
-                    ptx::mbar_wait(&acc_full[ab], w & 1, status, 232);
-                    ptx::tc_fence_after();
-                    k2_epilogue(prev, tmem + ab * 64, X, scale, partial, red, bar_ep, gt, warp, g);
-                    ptx::tc_fence_before();
-                    ptx::mbar_arrive(&acc_empty[ab]);
-                }
+                acc_par ^= (1u << m.nb) - 1u;
             }
-            prev = t;
         }
-        if (my_tiles > 0 && ((my_tiles - 1) & 1) == grp && gt < 256) {
-            const int pk = my_tiles - 1, ab = pk & 1, w = pk >> 1;
-            ptx::mbar_wait(&acc_full[ab], w & 1, status, 233);
+    } else if (warp != 18) {
+        // ================= the two box-sum sets ==================================================================
+        const bool is_a = warp < 8 || warp == 19;
+        const int gt = warp == 19 ? 256 + lane : (is_a ? tid : tid - 256);     // thread within its set
+        const int bar_ep = is_a ? 7 : 8;                        // named barrier of the set's drains (256 threads; 1-5 hand blocks over)
+        float* red = reinterpret_cast<float*>(sm + k2m::RED) + (is_a ? 0 : 256);
+        const int q = gt & 7, col = gt >> 3;                    // 8-dim chunk; column (A: of the 34 R columns, B: of the 32)
+        uint32_t it = 0, v = 0, acc_par = 0, prev_par = 0;
+        MacroTile prev;
+        prev.nb = 0;
+        prev.b = prev.mx0 = prev.my0 = prev.tile0 = 0;
+        // the tile of macro tile `mt` in accumulator b: the epilogue, by the first 256 threads of the set
+        auto drain = [&](const MacroTile& mt, int b, uint32_t par) {
+            CaTile t;
+            t.b = mt.b; t.ty0 = mt.my0 + b * k2m::BR; t.tx0 = mt.mx0;
+            t.index = mt.b * tiles_per_grid + mt.tile0 + b * strips;
+            // the state's values are requested before anything is waited for: the loads are the long latency here
+            __nv_bfloat16* pc = k2_epilogue_cell<5>(t, X, gt, warp, g);
+            uint4 xin[4] = {};
+            if (pc) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) xin[i] = reinterpret_cast<const uint4*>(pc)[i];
+            }
+            ptx::bar_sync(bar_ep, 256);      // the drain before this one is done with the reduction scratch
+            ptx::mbar_wait(&acc_full[b], (par >> b) & 1, status, 232);
             ptx::tc_fence_after();
-            k2_epilogue(prev, tmem + ab * 64, X, scale, partial, red, bar_ep, gt, warp, g);
+            k2_epilogue<5>(t, tmem + b * 64, pc, xin, scale, partial, red, bar_ep, gt, warp, g);
             ptx::tc_fence_before();
-            ptx::mbar_arrive(&acc_empty[ab]);
+            ptx::mbar_arrive(&acc_empty[b]);
+        };
+        const int mine = is_a ? 0 : 1;       // parity of the accumulators this set drains
+        V8 h2 = v8_zero(), h1 = v8_zero();   // running horizontal sums of the two rows above (of E in A, of R in B)
+        uint4 ekeep0 = make_uint4(0, 0, 0, 0), ekeep1 = ekeep0;   // B: centre E of the last two rows of the block before
+        const size_t vplane = (size_t)g.H * g.W * HD;
+        for (int k = 0; k < my_mt; ++k) {
+            const MacroTile m = macro_tile(blockIdx.x + k * gridDim.x, mt_per_grid, strips, g.H, nbmax);
+            for (int h = 0; h < NH; ++h) {
+                for (int b = -1; b < m.nb; ++b, ++it) {
+                    const int s = it % k2m::NSTAGE;
+                    uint8_t* es = sm + k2m::STG + s * k2m::STAGE_BYTES;     // [4][36] cells x 128 B
+                    uint8_t* vs = es + k2m::E_BYTES;                        // [4][34] cells: V, then R in place
+                    // the macro tile before: its accumulator b is drained before this one's first head overwrites it
+                    if (h == 0 && b >= 0 && b < prev.nb && (b & 1) == mine && gt < 256) drain(prev, b, prev_par);
+                    if (is_a) {
+                        // ---- A: R = V / box3(E) for the block's four V rows, marching down ----
+                        ptx::mbar_wait(&full[s], (it / k2m::NSTAGE) & 1, status, 230);
+                        if (col < k2m::VW) {
+#pragma unroll
+                            for (int j = 0; j < k2m::BR; ++j) {
+                                const uint8_t* row = es + (j * k2m::EW + col) * 128 + q * 16;
+                                const uint4 e0 = *reinterpret_cast<const uint4*>(row);
+                                const uint4 e1 = *reinterpret_cast<const uint4*>(row + 128);
+                                const uint4 e2 = *reinterpret_cast<const uint4*>(row + 256);
+                                const V8 hs = v8_sum3(e0, e1, e2);
+                                if (b >= 0 || j >= 2) {      // block -1: only its last two rows have all three E rows
+                                    uint4* pv = reinterpret_cast<uint4*>(vs + (j * k2m::VW + col) * 128 + q * 16);
+                                    *pv = v8_pack(v8_mul(v8_unpack(*pv), v8_rcp(v8_add(v8_add(h2, h1), hs))));
+                                }
+                                h2 = h1; h1 = hs;
+                            }
+                        }
+                        ptx::bar_arrive(1 + s, k2m::HANDOFF);       // R of this block is in the stage
+                    } else {
+                        // ---- B: V' = E * box3(R) for tile rows 4b .. 4b+3 -> A operand ----
+                        const int buf = v & 1;
+                        uint8_t* a_vp = sm + k2m::A_VP + buf * 16384;
+                        ptx::bar_sync(1 + s, k2m::HANDOFF);
+                        if (b >= 0) ptx::mbar_wait(&vp_empty[buf], ((v >> 1) & 1) ^ 1, status, 231);   // its last UMMAs are done
+                        const uint8_t* ecol = es + (col + 2) * 128 + q * 16;      // this thread's column in the E rows
+#pragma unroll
+                        for (int j = 0; j < k2m::BR; ++j) {
+                            if (b >= 0 || j >= 2) {
+                                const uint8_t* row = vs + (j * k2m::VW + col) * 128 + q * 16;
+                                const uint4 a0 = *reinterpret_cast<const uint4*>(row);
+                                const uint4 a1 = *reinterpret_cast<const uint4*>(row + 128);
+                                const uint4 a2 = *reinterpret_cast<const uint4*>(row + 256);
+                                const V8 hs = v8_sum3(a0, a1, a2);
+                                if (b >= 0) {
+                                    // tile row j is macro-tile row 4b+j: its E came with the block before (j < 2, kept
+                                    // in registers) or is row j-2 of this block's E rows
+                                    const V8 e = v8_unpack(j == 0 ? ekeep0 : j == 1 ? ekeep1
+                                                           : *reinterpret_cast<const uint4*>(ecol + (j - 2) * k2m::EW * 128));
+                                    const uint4 out = v8_pack(v8_mul(e, v8_add(v8_add(h2, h1), hs)));
+                                    *reinterpret_cast<uint4*>(a_vp + swz(j * k2m::SW + col, q)) = out;
+                                    const int orow = m.my0 + 4 * b + j, ocol = m.mx0 + col;
+                                    if (vprime != nullptr && orow < g.H && ocol < g.W)
+                                        *reinterpret_cast<uint4*>(vprime + ((size_t)m.b * NH + h) * vplane +
+                                                                  ((size_t)orow * g.W + ocol) * HD + q * 8) = out;
+                                }
+                                h2 = h1; h1 = hs;
+                            }
+                        }
+                        ekeep0 = *reinterpret_cast<const uint4*>(ecol + 2 * k2m::EW * 128);
+                        ekeep1 = *reinterpret_cast<const uint4*>(ecol + 3 * k2m::EW * 128);
+                        if (b >= 0) {
+                            ptx::fence_proxy_async();
+                            ptx::mbar_arrive(&vp_full[buf]);
+                            ++v;
+                        }
+                        ptx::mbar_arrive(&empty[s]);
+                    }
+                }
+                // accumulators of the macro tile before that this one does not reach (it has fewer blocks)
+                if (h == 0 && gt < 256)
+                    for (int b = m.nb; b < prev.nb; ++b)
+                        if ((b & 1) == mine) drain(prev, b, prev_par);
+            }
+            prev = m;
+            prev_par = acc_par;
+            acc_par ^= (1u << m.nb) - 1u;
         }
+        if (gt < 256)
+            for (int b = 0; b < prev.nb; ++b)
+                if ((b & 1) == mine) drain(prev, b, prev_par);
     }
     ptx::tc_fence_before();
     __syncthreads();
-    if (warp == 0) ptx::tmem_dealloc(tmem, k2b::TMEM_COLS);
+    if (warp == 0) ptx::tmem_dealloc(tmem, k2m::TMEM_COLS);
 }
 
 // =============================================================================================================
@@ -763,7 +859,8 @@ inline const char* bf16_error() { return bf16_error_ref(); }
 inline void bf16_plan(Bf16Plan& p, const Geom& g) {
     p.tiles_x = (g.W + TBW - 1) / TBW;
     p.k1_tiles = p.tiles_x * ((g.H + 2 * g.he + TBH - 1) / TBH);
-    p.k2_tiles = p.tiles_x * ((g.H + TBH - 1) / TBH);
+    p.strips = (g.W + k2m::SW - 1) / k2m::SW;
+    p.k2_tiles = p.strips * ((g.H + k2m::BR - 1) / k2m::BR);      // one partial per 4 x 32 tile
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -810,7 +907,7 @@ inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16*
         bf16_error_ref() = "cuTensorMapEncodeTiled rejected the weight layout";
         return -1;
     }
-    if (make_plane_map(enc, &p.map_e, E, g, TBW + 4, TBH + 4) || make_plane_map(enc, &p.map_v, V, g, TBW + 2, TBH + 2) ||
+    if (make_plane_map(enc, &p.map_e, E, g, k2m::EW, k2m::BR) || make_plane_map(enc, &p.map_v, V, g, k2m::VW, k2m::BR) ||
         make_plane_map(enc, &p.st.e, E, g, TBW, TBH, CU_TENSOR_MAP_SWIZZLE_128B) ||
         make_plane_map(enc, &p.st.v, V, g, TBW, TBH, CU_TENSOR_MAP_SWIZZLE_128B) ||
         make_plane_map(enc, &p.st.e_col, E, g, APRON, TBH, CU_TENSOR_MAP_SWIZZLE_128B) ||
@@ -825,13 +922,26 @@ inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16*
     p.k1_aligned = g.W % TBW == 0 && (!g.wrap_y || g.H % TBH == 0);
     if (cudaFuncSetAttribute(k1_bf16<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, k1b::SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(k1_bf16<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, k1b::SMEM) != cudaSuccess ||
-        cudaFuncSetAttribute(k2_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, k2b::SMEM) != cudaSuccess) {
+        cudaFuncSetAttribute(k2_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, k2m::SMEM) != cudaSuccess) {
         bf16_error_ref() = "could not opt in to the kernels' dynamic shared memory";
         return -1;
     }
-    const long long total = (long long)p.k2_tiles * g.B, total1 = (long long)p.k1_tiles * g.B;
-    p.k2_grid = (int)(total < num_sms ? total : num_sms);
+    const long long total1 = (long long)p.k1_tiles * g.B;
     p.k1_grid = (int)(total1 < num_sms ? total1 : num_sms);
+    // k2: blocks per macro tile.  A taller macro tile re-primes its march less often (nb + 1 blocks of work for nb
+    // tiles) but gives fewer, coarser units to spread over the SMs: take the height with the best product of the two.
+    long long total_mt = 0;
+    double best = -1.0;
+    const int rows4 = (g.H + k2m::BR - 1) / k2m::BR;
+    for (int nb = k2m::NB; nb >= 1; nb >>= 1) {
+        const int mt_rows = (rows4 + nb - 1) / nb;
+        const long long total = (long long)p.strips * mt_rows * g.B;
+        const double per_mt = (double)rows4 / mt_rows;                         // tiles per macro tile on average
+        const long long waves = (total + num_sms - 1) / num_sms;
+        const double eff = per_mt / (per_mt + 1.0) * (double)total / (double)(waves * num_sms);
+        if (eff > best) { best = eff; p.nbmax = nb; p.mt_per_grid = p.strips * mt_rows; total_mt = total; }
+    }
+    p.k2_grid = (int)(total_mt < num_sms ? total_mt : num_sms);
     return 0;
 }
 
@@ -848,8 +958,8 @@ inline int bf16_k1(Bf16Plan& p, const __nv_bfloat16* X, const float* scale, cons
 
 inline int bf16_k2(Bf16Plan& p, __nv_bfloat16* X, const float* scale, const __nv_bfloat16*, const __nv_bfloat16*,
                    float* partial, __nv_bfloat16* vprime, int* status, const Geom& g, cudaStream_t st) {
-    k2_bf16<<<p.k2_grid, k2b::THREADS, k2b::SMEM, st>>>(p.map_wo, p.map_e, p.map_v, X, scale, partial, vprime, status,
-                                                        p.k2_tiles * g.B, p.k2_tiles, g);
+    k2_bf16<<<p.k2_grid, k2m::THREADS, k2m::SMEM, st>>>(p.map_wo, p.map_e, p.map_v, X, scale, partial, vprime, status,
+                                                        p.mt_per_grid * g.B, p.mt_per_grid, p.strips, p.k2_tiles, p.nbmax, g);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }
 

@@ -18,7 +18,7 @@ namespace slime {
 constexpr int T32 = 8;                 // tile edge of the fp32 kernels (64 cells)
 constexpr int XS32 = 68;               // padded cell stride in floats (keeps float4 alignment, breaks bank ties)
 constexpr int K1F32_SMEM = (100 * XS32 + 64 * XS32 + 64 * 192 + 16) * 4;
-constexpr int K2F32_SMEM = (144 * 64 + 100 * 64 + 64 * XS32 + 64 * 64 + 16 * 64) * 4;
+constexpr int K2F32_SMEM = (144 * 64 + 100 * 64 + 64 * XS32 + 64 * 64 + 2 * 16 * 64) * 4;   // the last term: [16][64] doubles
 
 __global__ void __launch_bounds__(256)
 k1_f32(const float* __restrict__ X, const float* __restrict__ scale, const float* __restrict__ Wpiv,
@@ -126,14 +126,14 @@ k1_f32(const float* __restrict__ X, const float* __restrict__ scale, const float
 
 __global__ void __launch_bounds__(256)
 k2_f32(float* __restrict__ X, const float* __restrict__ scale, const float* __restrict__ Wo,
-       const float* __restrict__ E, const float* __restrict__ V, float* __restrict__ partial,
+       const float* __restrict__ E, const float* __restrict__ V, float* __restrict__ partial, size_t lo_offset,
        float* __restrict__ vprime, Geom g) {
     extern __shared__ __align__(16) float sm[];
     float* es = sm;                    // [12*12][64]  E with a 2-cell halo
     float* vs = es + 144 * 64;         // [10*10][64]  V, then R = V / box3(E), with a 1-cell halo
     float* vp = vs + 100 * 64;         // [64][XS32]   V' of the tile
     float* wo = vp + 64 * XS32;        // [64][64]     Wo rows of the current head
-    float* red = wo + 64 * 64;         // [16][64]
+    double* red = reinterpret_cast<double*>(wo + 64 * 64);   // [16][64] fp64 (the offset is a multiple of 8 bytes)
 
     const int tid = threadIdx.x;
     const int b = blockIdx.y;
@@ -224,7 +224,10 @@ k2_f32(float* __restrict__ X, const float* __restrict__ scale, const float* __re
 
     // X+ = scale * X + dt * Y, in place, and the tile's per-channel sums of what was stored
     const float4 s = *reinterpret_cast<const float4*>(scale + b * NC + c0);
-    float4 psum = make_float4(0.f, 0.f, 0.f, 0.f);
+    // The tile's channel sums are kept in fp64 and handed on as a float pair (value, remainder): a state that has
+    // grown large and signed makes the per-channel sum a small difference of large terms, and fp32 tile sums would
+    // then miss the 1e-6 bound on the renormalised mass.
+    double psum[4] = {0.0, 0.0, 0.0, 0.0};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
         const int cell = cg * 4 + j;
@@ -235,15 +238,19 @@ k2_f32(float* __restrict__ X, const float* __restrict__ scale, const float* __re
         v.x = fmaf(g.dt, acc[j][0], v.x * s.x); v.y = fmaf(g.dt, acc[j][1], v.y * s.y);
         v.z = fmaf(g.dt, acc[j][2], v.z * s.z); v.w = fmaf(g.dt, acc[j][3], v.w * s.w);
         *reinterpret_cast<float4*>(px) = v;
-        psum.x += v.x; psum.y += v.y; psum.z += v.z; psum.w += v.w;
+        psum[0] += (double)v.x; psum[1] += (double)v.y; psum[2] += (double)v.z; psum[3] += (double)v.w;
     }
-    *reinterpret_cast<float4*>(red + cg * 64 + c0) = psum;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) red[cg * 64 + c0 + k] = psum[k];
     __syncthreads();
     if (tid < 64) {
-        float t = 0.f;
+        double t = 0.0;
 #pragma unroll
         for (int k = 0; k < 16; ++k) t += red[k * 64 + tid];
-        partial[((size_t)b * gridDim.x + blockIdx.x) * NC + tid] = t;
+        const size_t o = ((size_t)b * gridDim.x + blockIdx.x) * NC + tid;
+        const float hi = (float)t;
+        partial[o] = hi;
+        partial[o + lo_offset] = (float)(t - (double)hi);
     }
 }
 

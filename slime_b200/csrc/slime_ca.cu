@@ -39,6 +39,7 @@ struct slime_ca {
     double* sums = nullptr;
     float* partial = nullptr;
     int partial_cap = 0;
+    size_t partial_lo = 0;          // fp32 path: offset (floats) of the remainders of the step's tile sums
     double* seg_sums = nullptr;
     int k1_tiles = 0, k2_tiles = 0, tiles_x = 0;
     // weights
@@ -154,12 +155,12 @@ int step_kernels(slime_ca* h, void* emit, cudaStream_t st, cudaEvent_t* ev = nul
         LAUNCHED(h);
         if (ev) CK(h, cudaEventRecord(ev[1], st));
         k2_f32<<<dim3(h->k2_tiles, g.B), 256, K2F32_SMEM, st>>>((float*)h->X, h->scale, h->wo_f32, (const float*)h->E,
-                                                                 (const float*)h->V, h->partial, (float*)emit, g);
+                                                                 (const float*)h->V, h->partial, h->partial_lo, (float*)emit, g);
         LAUNCHED(h);
     }
     if (ev) CK(h, cudaEventRecord(ev[2], st));
     const int nseg = h->k2_tiles < 64 ? h->k2_tiles : 64;
-    k_reduce_partials<<<dim3(nseg, g.B), 256, 0, st>>>(h->partial, h->k2_tiles, h->seg_sums);
+    k_reduce_partials<<<dim3(nseg, g.B), 256, 0, st>>>(h->partial, h->k2_tiles, h->seg_sums, is_bf16(h) ? 0 : h->partial_lo);
     LAUNCHED(h);
     k_finish_sums<<<g.B, 64, 0, st>>>(h->seg_sums, nseg, h->sums, h->mass, h->scale, 0);
     LAUNCHED(h);
@@ -343,7 +344,8 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
     if ((rc = dev_alloc(h, &h->scale, (size_t)g.B * NC))) return rc;
     if ((rc = dev_alloc(h, &h->mass, (size_t)g.B * NC))) return rc;
     if ((rc = dev_alloc(h, &h->sums, (size_t)g.B * NC))) return rc;
-    if ((rc = dev_alloc(h, &h->partial, (size_t)g.B * h->partial_cap * NC))) return rc;
+    h->partial_lo = is_bf16(h) ? 0 : (size_t)g.B * h->partial_cap * NC;
+    if ((rc = dev_alloc(h, &h->partial, (size_t)g.B * h->partial_cap * NC + h->partial_lo))) return rc;
     if ((rc = dev_alloc(h, &h->seg_sums, (size_t)g.B * 64 * NC))) return rc;
     if ((rc = dev_alloc(h, &h->dev_status, 1))) return rc;
     CK(h, cudaMemset(h->dev_status, 0, sizeof(int)));
@@ -1123,10 +1125,10 @@ int slime_ca_occupancy(slime_ca* h, float* occupancy) {
     CK(h, cudaDeviceGetAttribute(&max_threads, cudaDevAttrMaxThreadsPerMultiProcessor, h->cfg.device));
     int b1 = 0, b2 = 0, t1, t2;
     if (is_bf16(h)) {
-        t1 = k1b::THREADS; t2 = k2b::THREADS;
+        t1 = k1b::THREADS; t2 = k2m::THREADS;
         if (h->bf.k1_aligned) CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b1, k1_bf16<true>, t1, k1b::SMEM));
         else CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b1, k1_bf16<false>, t1, k1b::SMEM));
-        CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b2, k2_bf16, t2, k2b::SMEM));
+        CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b2, k2_bf16, t2, k2m::SMEM));
     } else {
         t1 = t2 = 256;
         CK(h, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&b1, k1_f32, t1, K1F32_SMEM));

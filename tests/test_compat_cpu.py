@@ -85,3 +85,21 @@ def test_output_projection_folds_the_reference_head_mixing():
         # the reference kernel itself: out[o][c] = sum_in mixing[o][in] * v[in][c]
         assert np.abs(out - mix.astype(np.float64) @ v.reshape(8, 64)).max() < 1e-6
         assert np.abs(v @ Wo.astype(np.float64) - out.mean(axis=0)).max() < 1e-6
+
+
+def test_genome_hash_matches_the_reference_kernel():
+    """tests/golden/ref_elite.json holds what the reference's own create_elite_kernel (slime/memory/archive.cu:66-82,
+    run on a B200 by oracle/ref_elite_harness.cu) wrote for four seeded genomes; the restated hash reproduces every
+    genome_hash, and the record keeps fitness, coherence, effective rank and generation as given."""
+    import json
+    import struct
+    from oracle import ca_oracle
+    z = json.load(open(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_elite.json")))
+    assert len(z["cases"]) == 4
+    for i, c in enumerate(z["cases"]):
+        genome = np.array(c["genome"], dtype=np.uint32).view(np.float32)
+        assert ca_oracle.genome_hash(genome) == int(c["genome_hash"])
+        as_f = lambda u: struct.unpack("<f", struct.pack("<I", u))[0]
+        assert as_f(c["fitness"]) == 1.5 + i and as_f(c["coherence"]) == 0.25 * i and as_f(c["effective_rank"]) == 6.0 - i
+        assert c["generation"] == 40 + 1000 * i
+    assert any(u >= 0x80000000 for c in z["cases"] for u in c["genome"])      # negative values: the 32-bit sum wraps
