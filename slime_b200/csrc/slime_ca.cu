@@ -59,6 +59,7 @@ struct slime_ca {
     // fitness scratch
     double* gram_part = nullptr;
     int gram_splits = 0;
+    CUtensorMap gram_map[2];        // bf16 path: tensor maps over the two V' buffers for the tensor-core Gram
     float* head_rank = nullptr;
     double* pearson_part = nullptr;
     int pearson_splits = 0;
@@ -335,6 +336,10 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
         if ((size_t)h->gram_splits * GRAM_CHUNK < cells)
             return fail(h, SLIME_CA_EINVAL, "keep_vprime supports grids of at most 131072 cells");
         if ((rc = dev_alloc(h, &h->gram_part, (size_t)g.B * NH * h->gram_splits * HD * HD))) return rc;
+        if (is_bf16(h))
+            for (int i = 0; i < 2; ++i)
+                if (gram_tc_map(&h->gram_map[i], h->vprime[i], g.B * NH, (int)cells) != 0)
+                    return fail(h, SLIME_CA_ECUDA, "tensor-map set-up of the Gram kernel failed");
         if ((rc = dev_alloc(h, &h->head_rank, (size_t)g.B * NH))) return rc;
         h->pearson_splits = (int)((cells * HC + 262143) / 262144);
         if (h->pearson_splits > 64) h->pearson_splits = 64;
@@ -617,7 +622,7 @@ int slime_ca_fitness(slime_ca* h, float* rank, float* coherence, float* fitness,
     const void* vb = h->vprime[h->vp_last];
     const size_t per_grid = (size_t)cells * HC;
     if (is_bf16(h)) {
-        k_gram<__nv_bfloat16><<<dim3(h->gram_splits, NH, g.B), GRAM_THREADS, 0, st>>>((const __nv_bfloat16*)vb, cells, h->gram_part);
+        k_gram_tc<<<g.B * NH, 128, gtc::SMEM, st>>>(h->gram_map[h->vp_last], cells, h->gram_splits, h->gram_part, h->dev_status);
         LAUNCHED(h);
         k_pearson<__nv_bfloat16><<<dim3(h->pearson_splits, g.B), 256, 0, st>>>((const __nv_bfloat16*)va, (const __nv_bfloat16*)vb, per_grid, h->pearson_part);
         LAUNCHED(h);
