@@ -86,23 +86,26 @@ class ClockSampler(threading.Thread):
 
 def ncu_dram_bytes_per_cell(kernel):
     """DRAM bytes per cell-update of a bf16 kernel, read from the ncu summary committed under profiles/
-    (dram__bytes_read.sum + dram__bytes_write.sum of one captured launch over the cells of that launch).  The capture is
-    a batch of 8 grids (268 MB of E/V per kernel, larger than L2); traffic grows in proportion to the cells, so a full
-    launch is this figure times its cells.  k1's figure sits below its algorithmic bytes because part of what it wrote
-    was still dirty in the 126 MB L2 when the captured launch ended.  None if the summary is missing or unreadable."""
+    (dram__bytes_read.sum + dram__bytes_write.sum of one captured launch over the cells of that launch) -> (bytes per
+    cell, file name), or (None, None) if there is no readable summary.  The captures are batches of 8 or 16 grids (a
+    quarter to half a GB of E/V per kernel, larger than L2); traffic grows in proportion to the cells, so a full launch
+    is this figure times its cells.  k1's figure sits below its algorithmic bytes because part of what it wrote was still
+    dirty in the 126 MB L2 when the captured launch ended."""
+    import glob
     import re
-    path = os.path.join(ROOT, "profiles", f"{kernel}_bf16_batch8_128x128.txt")
-    try:
-        text = open(path).read()
-        cells = int(re.search(r"one launch = ([\d ]+) cells", text).group(1).replace(" ", ""))
-        unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
-        total = 0.0
-        for name in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
-            m = re.search(r"^" + re.escape(name) + r"\s+([\d.]+)\s+(\w+)", text, re.M)
-            total += float(m.group(1)) * unit[m.group(2)]
-        return total / cells
-    except (OSError, AttributeError, KeyError, ValueError):
-        return None
+    for path in sorted(glob.glob(os.path.join(ROOT, "profiles", f"{kernel}_bf16_batch*_128x128.txt"))):
+        try:
+            text = open(path).read()
+            cells = int(re.search(r"one launch = ([\d ]+) cells", text).group(1).replace(" ", ""))
+            unit = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9}
+            total = 0.0
+            for name in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+                m = re.search(r"^" + re.escape(name) + r"\s+([\d.]+)\s+(\w+)", text, re.M)
+                total += float(m.group(1)) * unit[m.group(2)]
+            return total / cells, os.path.basename(path)
+        except (OSError, AttributeError, KeyError, ValueError):
+            continue
+    return None, None
 
 
 def cpu_baseline(ca_steps_sample=2, grids=1):
@@ -243,10 +246,10 @@ def main():
     dom_ms = max(kt[0], kt[1]) / S
     peak, tensor_peak, peak_kind = measured_peaks()
     achieved = cells * ALG_BYTES[dom][args.dtype] / (dom_ms * 1e-3) / 1e9
-    per_cell = ncu_dram_bytes_per_cell(dom) if args.dtype == "bf16" else None
+    per_cell, per_cell_file = ncu_dram_bytes_per_cell(dom) if args.dtype == "bf16" else (None, None)
     roofline = {"bound": "hbm", "kernel": dom + "_" + args.dtype, "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "traffic": None if per_cell is None else cells * per_cell, "peak_kind": peak_kind,
-                "traffic_source": f"profiles/{dom}_bf16_batch8_128x128.txt scaled by cells" if per_cell else None,
+                "traffic_source": f"profiles/{per_cell_file} scaled by cells" if per_cell else None,
                 "algorithmic_bytes_per_launch": cells * ALG_BYTES[dom][args.dtype],
                 "ms_per_launch": dom_ms, "k1_ms": kt[0] / S, "k2_ms": kt[1] / S, "other_ms": kt[2] / S,
                 "k1_frac": cells * ALG_BYTES["k1"][args.dtype] / (kt[0] / S * 1e-3) / 1e9 / peak,
