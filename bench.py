@@ -108,6 +108,17 @@ def ncu_dram_bytes_per_cell(kernel):
     return None, None
 
 
+def bench_config(batch, ca_steps, dtype, world):
+    """The `config` object of the bench line: the same for this library's arm and for the reference arm."""
+    cells = batch * GRID * GRID
+    return {"workload": f"batched training-shape forward X[{batch},{GRID},{GRID},64] per GPU, 8 heads x 64, "
+                        f"{ca_steps} CA steps per bench step, renorm every step",
+            "weights": "specified draws, output projection made mass-neutral so the trajectory stays finite",
+            "l2": "working set per step (E,V intermediates %.1f GB) exceeds the 126 MB L2" %
+                  (2 * cells * 512 * (2 if dtype == "bf16" else 4) / 1e9),
+            "parallelism": f"batch-sharded x{world}, no data-path collective"}
+
+
 def cpu_baseline(ca_steps_sample=2, grids=1):
     """The oracle's fp32 multithreaded transcription on a bounded sample: `grids` grids x `ca_steps_sample` steps."""
     from oracle import ca_oracle
@@ -141,9 +152,9 @@ def run_reference(args, rank, world):
             "warmup": args.warmup, "ms_per_step": float(np.mean(secs)) * 1e3,       # what a (sampled) step really took
             "ms_per_full_step_extrapolated": BATCH * GRID * GRID * CA_STEPS / v * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"batched training-shape forward X[{BATCH},{GRID},{GRID},64], 8 heads x 64, {CA_STEPS} CA steps "
-                                   "per bench step (each step times 2 of the 64 grids for all 64 CA steps; rate extrapolated)",
-                       "inputs": "seeded synthetic"},
+            # the workload of this library's arm; each step of this arm times a bounded sample of it (2 of the 64 grids
+            # for all 64 CA steps, see cpu_baseline.sample) and the rate is that of the sample
+            "config": bench_config(BATCH, CA_STEPS, "bf16", args.gpus),
             "cpu_baseline": base,
             "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
@@ -280,12 +291,7 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
                 "vs_baseline": None, "dtype": args.dtype, "data": "synthetic",
-                "config": {"workload": f"batched training-shape forward X[{B},{GRID},{GRID},64] per GPU, 8 heads x 64, "
-                                       f"{S} CA steps per bench step, renorm every step",
-                           "weights": "specified draws, output projection made mass-neutral so the trajectory stays finite",
-                           "l2": "working set per step (E,V intermediates %.1f GB) exceeds the 126 MB L2" %
-                                 (2 * cells * 512 * (2 if args.dtype == "bf16" else 4) / 1e9),
-                           "parallelism": f"batch-sharded x{world}, no data-path collective"},
+                "config": bench_config(B, S, args.dtype, world),
                 "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline,
                 "state_after_last_timed_forward": state_check, "stripe": stripe}
         if not args.no_cpu_baseline and world == 1:       # the CPU baseline is timed at N = 1 only

@@ -179,3 +179,32 @@ def test_activation_beyond_the_clamp_is_the_same_function_everywhere(gpu):
             got = h.get_state()
         assert np.isfinite(got).all()
         assert rel_l2(got, ref) < tol
+
+
+@pytest.mark.parametrize("dtype_name", ["f32", "bf16"])
+def test_population_shape_32_steps_and_fitness(gpu, dtype_name):
+    """The population workload's shape in small: 4 weight sets x 2 grids of 64 x 64, each set with its own seeded
+    weights, all 32 steps, then the fitness of every grid from the last two steps."""
+    from oracle import ca_oracle
+    capi, devmem = gpu
+    steps, n_sets, per = 32, 4, 2
+    X0 = inputs.make_state(n_sets * per, 64, 64, seed=42)
+    w = inputs.make_weight_sets(n_sets, seed=42, bounded=True)
+    R1, rprev, rlast = truth("population", lambda: ca_oracle.ca_steps(X0, w, steps, literal=False, want_vprime=True))
+    with capi.Handle(n_sets * per, 64, 64, n_weight_sets=n_sets, dtype=capi.F32 if dtype_name == "f32" else capi.BF16,
+                     keep_vprime=True) as h:
+        h.set_weights(w)
+        h.set_state(X0)
+        h.step(steps)
+        X1, fit = h.get_state(), h.fitness()
+    assert np.isfinite(X1).all()
+    assert rel_l2(X1, R1) < state_tolerance(dtype_name, X0, w, steps, R1)
+    check_mass(dtype_name, X0, X1)
+    ref = ca_oracle.fitness(rprev, rlast)
+    if dtype_name == "f32":
+        for k in ("rank", "coherence", "fitness", "hunger"):
+            np.testing.assert_allclose(fit[k], ref[k], atol=1e-4)
+    else:
+        np.testing.assert_allclose(fit["rank"], ref["rank"], rtol=5e-2)
+        np.testing.assert_allclose(fit["coherence"], ref["coherence"], atol=2e-2)
+    assert len(set(np.round(ref["rank"], 3))) > 1          # different weight sets, different ranks: the grouping matters
