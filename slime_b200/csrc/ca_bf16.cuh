@@ -45,6 +45,7 @@ struct Bf16Plan {
     CUtensorMap map_wo;   // [sets*8*64][64]  bf16, box 64 x 64,  128B swizzle
     CUtensorMap map_e;    // E planes [B*8][H+4][W+4][64], box 64 x 36 x 4 x 1 (a block of k2)
     CUtensorMap map_v;    // V planes, box 64 x 34 x 4 x 1
+    CUtensorMap map_x;    // the state's own rows (and the halo rows above them) [B][hx + H][W][64], box 64 x 32 x 4 x 1, 128B swizzle
     K1StoreMaps st;       // store maps of k1 (whole tile, last two columns, last two rows, their corner)
     bool k1_aligned = false;
     int strips = 1, mt_per_grid = 1, nbmax = 8;    // k2: 32-column strips, macro tiles per grid, blocks per macro tile
@@ -478,40 +479,31 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
 
 // Epilogue of one finished tile, run by 8 warps (256 threads) of one compute group: X+ = scale*X + dt*Y in
 // place, and the tile's per-channel sums of the stored (rounded) values -> partial[tile][64].
-// Epilogue of a finished tile.  WSHIFT: the tile is (128 >> WSHIFT) rows of (1 << WSHIFT) cells, cell m of the tile in
-// TMEM lane m.
-// This thread's cell of a finished tile: where its 32 channels of X live (null when the cell lies outside the grid)
-template <int WSHIFT>
-__device__ __forceinline__ __nv_bfloat16* k2_epilogue_cell(const CaTile& t, __nv_bfloat16* __restrict__ X, int gt,
-                                                           int cta_warp, const Geom& g) {
+// Epilogue of a finished 4 x 32-cell tile (cell m of the tile = TMEM lane m), by 8 warps (256 threads): X+ = scale*X +
+// dt*Y, and the tile's per-channel sums of the stored (rounded) values -> partial[tile][64].  The tile's state sits in
+// shared memory, [128 cells][128 B] with the 128-byte swizzle, where a TMA load put it; X+ is written back in place
+// and leaves by a TMA store, so the warps never wait on global memory here.
+__device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr, uint8_t* xs,
+                                            const float* __restrict__ scale, float* __restrict__ partial,
+                                            float* red, int bar_id, int gt, int cta_warp, const Geom& g) {
     const int lane = gt & 31, quad = cta_warp & 3, half = (gt >> 5) >> 2;
     const int m = quad * 32 + lane;
-    const int r = t.ty0 + (m >> WSHIFT), x = t.tx0 + (m & ((1 << WSHIFT) - 1));
-    if (!(r < g.H && x < g.W)) return nullptr;
-    const size_t xplane = (size_t)g.state_rows() * g.W * NC;
-    return X + (size_t)t.b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC + half * 32;
-}
-// xin: the thread's 32 channels of X as loaded by the caller before it waited for the accumulator (4 x 16 bytes)
-template <int WSHIFT>
-__device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr, __nv_bfloat16* __restrict__ pcell,
-                                            const uint4 (&xin)[4], const float* __restrict__ scale,
-                                            float* __restrict__ partial, float* red, int bar_id, int gt, int cta_warp,
-                                            const Geom& g) {
-    const int lane = gt & 31, quad = cta_warp & 3, half = (gt >> 5) >> 2;
-    const bool valid = pcell != nullptr;
-    __nv_bfloat16* px = pcell - half * 32;
+    const int r = t.ty0 + (m >> 5), x = t.tx0 + (m & 31);
+    const bool valid = r < g.H && x < g.W;       // cells outside the grid: loaded as zeros, clipped by the store
     const float* sc = scale + t.b * NC;
 #pragma unroll
     for (int sub = 0; sub < 2; ++sub) {
-        const int c0 = half * 32 + sub * 16;
+        const int c0 = half * 32 + sub * 16, q0 = half * 4 + sub * 2;
         uint32_t ry[16];
         ptx::tmem_ld16(acc_taddr + ((uint32_t)(quad * 32) << 16) + c0, ry);
         ptx::tmem_ld_wait();
         float xo[16];
         if (valid) {
             float f0[8], f1[8], sv[16];
-            unpack8(xin[2 * sub], f0);
-            unpack8(xin[2 * sub + 1], f1);
+            uint4* p0 = reinterpret_cast<uint4*>(xs + swz(m, q0));
+            uint4* p1 = reinterpret_cast<uint4*>(xs + swz(m, q0 + 1));
+            unpack8(*p0, f0);
+            unpack8(*p1, f1);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const float4 s4 = __ldg(reinterpret_cast<const float4*>(sc + c0) + k);
@@ -529,8 +521,8 @@ __device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr,
                 xo[2 * k] = bf16_lo(pk[k]);          // sum what is stored, after rounding
                 xo[2 * k + 1] = bf16_hi(pk[k]);
             }
-            *reinterpret_cast<uint4*>(px + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-            *reinterpret_cast<uint4*>(px + c0 + 8) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            *p0 = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *p1 = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         } else {
 #pragma unroll
             for (int k = 0; k < 16; ++k) xo[k] = 0.f;
@@ -552,6 +544,7 @@ __device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr,
             red[quad * 64 + c0 + ch] = xo[0];
         }
     }
+    ptx::fence_proxy_async();      // X+ in shared memory, for the TMA store issued behind the barrier
     ptx::bar_sync(bar_id, 256);
     if (gt < NC) partial[(size_t)t.index * NC + gt] = (red[gt] + red[64 + gt]) + (red[128 + gt] + red[192 + gt]);
 }
@@ -564,7 +557,7 @@ __device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr,
 // both box sums in registers from block to block, so every E and V row of the strip is loaded and summed once per
 // head (square tiles with a 2-cell ring all round re-read 1.9x the E rows and 1.4x the V rows at 8 x 16 cells).  A
 // block is 4 rows of the strip: E rows with a 2-column ring (36 cells), V rows with a 1-column ring (34 cells), 35 KB,
-// in a 5-stage ring.  Block -1 of a march only primes the registers (E rows -2..1, R rows -1..0 of the macro tile).
+// in a 4-stage ring.  Block -1 of a march only primes the registers (E rows -2..1, R rows -1..0 of the macro tile).
 // The two box sums run on different warps, one block apart, with no barrier inside either set:
 //   warps 0-7,19 A: R = V / box3(E) in place in the stage, one thread per (column of the 34, 8 dims); hands the block
 //                to B through a named barrier it only arrives on
@@ -575,7 +568,9 @@ __device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr,
 // so that each of the SM's four schedulers (warp index mod 4) carries two A warps and two B warps, the half-filled
 // ninth A warp sits alone on the fourth, and the two single-thread roles on the first two.
 // The epilogue of a macro tile (X+ = scale X + dt Y, channel sums) is interleaved into the first head of the next one:
-// A's first eight warps drain the even accumulators, B the odd ones, each just before its own block of that tile.
+// A's first eight warps drain the even accumulators, B the odd ones, each just before its own block of that tile.  The
+// tile's state comes to the draining set by TMA (each set owns one 16 KB buffer, loaded one block ahead) and X+ leaves
+// by a TMA store from the same buffer.
 // Every cell's arithmetic is the same sequence of operations wherever the cell sits in a tile or a block, so shifting a
 // torus shifts the result bit for bit.
 // Eight fp32 values (the 8 dims a thread owns) as four packed pairs, and the few operations the box sums need on them
@@ -605,13 +600,14 @@ constexpr int EW = SW + 4, VW = SW + 2;                 // cells per E / V row o
 constexpr int E_BYTES = BR * EW * 128, V_BYTES = BR * VW * 128;
 constexpr int STAGE_BYTES = E_BYTES + V_BYTES;          // 35 840
 constexpr uint32_t STAGE_TX = STAGE_BYTES;
-constexpr int NSTAGE = 5;
+constexpr int NSTAGE = 4;
 constexpr int STG = 0;
 constexpr int A_VP = STG + NSTAGE * STAGE_BYTES;        // two 16 KB operand tiles
 constexpr int WO = A_VP + 2 * 16384;                    // two 8 KB Wo slices
-constexpr int RED = WO + 2 * 8192;                      // [A, B][4 quads][64] fp32
+constexpr int XT = WO + 2 * 8192;                       // two 16 KB state tiles of the epilogue (one per box-sum set)
+constexpr int RED = XT + 2 * 16384;                     // [A, B][4 quads][64] fp32
 constexpr int BARS = RED + 2 * 4 * 64 * 4;
-constexpr int N_BARS = NSTAGE + NSTAGE + 2 + 2 + 2 + 2 + NB + NB;
+constexpr int N_BARS = NSTAGE + NSTAGE + 2 + 2 + 2 + 2 + NB + NB + 2 + 2;
 constexpr int TMEM_PTR = BARS + N_BARS * 8;
 constexpr int BYTES = TMEM_PTR + 16;
 constexpr int SMEM = BYTES + 1024;
@@ -619,7 +615,7 @@ constexpr uint32_t TMEM_COLS = 512;
 constexpr int A_THREADS = 288, B_THREADS = 256;
 constexpr int THREADS = 640;                            // 20 warps, see the kernel for who does what
 constexpr int HANDOFF = A_THREADS + B_THREADS;          // parties of the named barrier that hands a block from A to B
-static_assert(STAGE_BYTES % 1024 == 0 && A_VP % 1024 == 0 && WO % 1024 == 0, "operand tiles must be 1024-byte aligned");
+static_assert(STAGE_BYTES % 1024 == 0 && A_VP % 1024 == 0 && WO % 1024 == 0 && XT % 1024 == 0, "swizzled tiles must be 1024-byte aligned");
 static_assert(SMEM <= 227 * 1024, "k2 (marching) shared memory");
 }  // namespace k2m
 
@@ -642,7 +638,7 @@ __device__ __forceinline__ MacroTile macro_tile(int idx, int per_grid, int strip
 
 __global__ void __launch_bounds__(k2m::THREADS, 1)
 k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUtensorMap map_e,
-              const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ X, const float* __restrict__ scale,
+              const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_x, const float* __restrict__ scale,
               float* __restrict__ partial, __nv_bfloat16* __restrict__ vprime, int* __restrict__ status, int n_mt,
               int mt_per_grid, int strips, int tiles_per_grid, int nbmax, Geom g) {
     extern __shared__ uint8_t smem_raw[];
@@ -656,6 +652,8 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
     uint64_t* wo_empty = wo_full + 2;                // [2] the head that used it is issued and done  (waits: TMA producer)
     uint64_t* acc_full = wo_empty + 2;               // [8] all 8 heads of the tile accumulated       (waits: who drains it)
     uint64_t* acc_empty = acc_full + k2m::NB;        // [8] drained (256 arrivals)                    (waits: UMMA issuer)
+    uint64_t* x_full = acc_empty + k2m::NB;          // [2] a set's state tile landed                 (waits: that set)
+    uint64_t* x_empty = x_full + 2;                  // [2] ... and its X+ has left shared memory      (waits: TMA producer)
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(sm + k2m::TMEM_PTR);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -667,8 +665,9 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
             ptx::mbar_init(&wo_full[i], 1); ptx::mbar_init(&wo_empty[i], 1);
         }
         for (int i = 0; i < k2m::NB; ++i) { ptx::mbar_init(&acc_full[i], 1); ptx::mbar_init(&acc_empty[i], 256); }
+        for (int i = 0; i < 2; ++i) { ptx::mbar_init(&x_full[i], 1); ptx::mbar_init(&x_empty[i], 1); }
         ptx::fence_barrier_init();
-        ptx::prefetch_tmap(&map_wo); ptx::prefetch_tmap(&map_e); ptx::prefetch_tmap(&map_v);
+        ptx::prefetch_tmap(&map_wo); ptx::prefetch_tmap(&map_e); ptx::prefetch_tmap(&map_v); ptx::prefetch_tmap(&map_x);
     }
     if (warp == 0) ptx::tmem_alloc(tmem_ptr, k2m::TMEM_COLS);
     ptx::tc_fence_before();
@@ -681,6 +680,18 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
         // ================= TMA producer ===================================================================
         if (lane == 0) {
             uint32_t it = 0, wit = 0;       // blocks and heads so far
+            uint32_t nx[2] = {0, 0};        // state tiles loaded for set A (even tiles) and set B (odd tiles)
+            MacroTile prev;
+            prev.nb = 0;
+            prev.b = prev.mx0 = prev.my0 = prev.tile0 = 0;
+            // the state of tile b of macro tile `mt` for the epilogue that drains it, into the draining set's buffer
+            auto load_x = [&](const MacroTile& mt, int b) {
+                const int xb = b & 1;
+                ptx::mbar_wait(&x_empty[xb], (nx[xb] & 1) ^ 1, status, 212);
+                ptx::mbar_expect_tx(&x_full[xb], 16384);
+                ptx::tma_load_4d(sm + k2m::XT + xb * 16384, &map_x, 0, mt.mx0, g.hx + mt.my0 + b * k2m::BR, mt.b, &x_full[xb]);
+                ++nx[xb];
+            };
             for (int k = 0; k < my_mt; ++k) {
                 const MacroTile m = macro_tile(blockIdx.x + k * gridDim.x, mt_per_grid, strips, g.H, nbmax);
                 const int set = m.b / g.per_set;
@@ -699,9 +710,15 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
                         // outside the tensor read as zero and only feed values nobody uses)
                         ptx::tma_load_4d(st, &map_e, 0, m.mx0, m.my0 + 4 * b + 4, plane, &full[s]);
                         ptx::tma_load_4d(st + k2m::E_BYTES, &map_v, 0, m.mx0 + 1, m.my0 + 4 * b + 3, plane, &full[s]);
+                        // tile b+1 of the macro tile before is drained ahead of block b+1 of this head: its state now
+                        if (h == 0 && b + 1 < prev.nb && b + 1 < m.nb) load_x(prev, b + 1);
                     }
+                    if (h == 0)
+                        for (int b = m.nb; b < prev.nb; ++b) load_x(prev, b);       // tiles this macro tile does not reach
                 }
+                prev = m;
             }
+            for (int b = 0; b < prev.nb; ++b) load_x(prev, b);                      // the last macro tile's
         }
     } else if (warp == 17) {
         // ================= UMMA issuer ====================================================================
@@ -743,23 +760,28 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
         prev.nb = 0;
         prev.b = prev.mx0 = prev.my0 = prev.tile0 = 0;
         // the tile of macro tile `mt` in accumulator b: the epilogue, by the first 256 threads of the set
+        uint32_t nxs = 0;                    // state tiles this set has drained
+        uint8_t* xs = sm + k2m::XT + (is_a ? 0 : 16384);
         auto drain = [&](const MacroTile& mt, int b, uint32_t par) {
             CaTile t;
             t.b = mt.b; t.ty0 = mt.my0 + b * k2m::BR; t.tx0 = mt.mx0;
             t.index = mt.b * tiles_per_grid + mt.tile0 + b * strips;
-            // the state's values are requested before anything is waited for: the loads are the long latency here
-            __nv_bfloat16* pc = k2_epilogue_cell<5>(t, X, gt, warp, g);
-            uint4 xin[4] = {};
-            if (pc) {
-#pragma unroll
-                for (int i = 0; i < 4; ++i) xin[i] = reinterpret_cast<const uint4*>(pc)[i];
-            }
             ptx::bar_sync(bar_ep, 256);      // the drain before this one is done with the reduction scratch
             ptx::mbar_wait(&acc_full[b], (par >> b) & 1, status, 232);
+            ptx::mbar_wait(&x_full[is_a ? 0 : 1], nxs & 1, status, 233);
             ptx::tc_fence_after();
-            k2_epilogue<5>(t, tmem + b * 64, pc, xin, scale, partial, red, bar_ep, gt, warp, g);
+            k2_epilogue(t, tmem + b * 64, xs, scale, partial, red, bar_ep, gt, warp, g);
+            if (gt == 0) {
+                // X+ of the tile back to the state in one store (rows and columns past the grid are clipped); the
+                // buffer goes back to the producer once the store has read it
+                ptx::tma_store_4d(&map_x, xs, 0, t.tx0, g.hx + t.ty0, t.b);
+                ptx::bulk_commit();
+                ptx::bulk_wait_read0();
+                ptx::mbar_arrive(&x_empty[is_a ? 0 : 1]);
+            }
             ptx::tc_fence_before();
             ptx::mbar_arrive(&acc_empty[b]);
+            ++nxs;
         };
         const int mine = is_a ? 0 : 1;       // parity of the accumulators this set drains
         V8 h2 = v8_zero(), h1 = v8_zero();   // running horizontal sums of the two rows above (of E in A, of R in B)
@@ -845,6 +867,7 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
         if (gt < 256)
             for (int b = 0; b < prev.nb; ++b)
                 if ((b & 1) == mine) drain(prev, b, prev_par);
+        if (gt == 0) ptx::bulk_wait0();      // this set's stores of X+ are complete
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -893,7 +916,7 @@ inline int make_plane_map(EncodeTiledFn enc, CUtensorMap* map, const void* base,
 
 // Tensor maps over the weight arrays and the E/V planes, and the kernels' shared-memory opt-in.  0 on success.
 inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16* wo, int sets, const __nv_bfloat16* E,
-                      const __nv_bfloat16* V, const Geom& g, int num_sms) {
+                      const __nv_bfloat16* V, const __nv_bfloat16* X, const Geom& g, int num_sms) {
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn ||
@@ -918,6 +941,20 @@ inline int bf16_setup(Bf16Plan& p, const __nv_bfloat16* w1, const __nv_bfloat16*
         make_plane_map(enc, &p.st.v_cor, V, g, APRON, APRON, CU_TENSOR_MAP_SWIZZLE_128B)) {
         bf16_error_ref() = "cuTensorMapEncodeTiled rejected the E/V plane layout";
         return -1;
+    }
+    {
+        // the state as k2's epilogue sees it: the rows below the own rows (a stripe's bottom halo) are left out of
+        // the tensor, so a store of a tile that hangs over the last own row is clipped there
+        const cuuint64_t dims[4] = {64, (cuuint64_t)g.W, (cuuint64_t)(g.hx + g.H), (cuuint64_t)g.B};
+        const cuuint64_t strides[3] = {128, (cuuint64_t)g.W * 128, (cuuint64_t)g.state_rows() * g.W * 128};
+        const cuuint32_t box[4] = {64, k2m::SW, k2m::BR, 1};
+        const cuuint32_t estr[4] = {1, 1, 1, 1};
+        if (enc(&p.map_x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<__nv_bfloat16*>(X), dims, strides, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            bf16_error_ref() = "cuTensorMapEncodeTiled rejected the state layout";
+            return -1;
+        }
     }
     p.k1_aligned = g.W % TBW == 0 && (!g.wrap_y || g.H % TBH == 0);
     if (cudaFuncSetAttribute(k1_bf16<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, k1b::SMEM) != cudaSuccess ||
@@ -958,7 +995,7 @@ inline int bf16_k1(Bf16Plan& p, const __nv_bfloat16* X, const float* scale, cons
 
 inline int bf16_k2(Bf16Plan& p, __nv_bfloat16* X, const float* scale, const __nv_bfloat16*, const __nv_bfloat16*,
                    float* partial, __nv_bfloat16* vprime, int* status, const Geom& g, cudaStream_t st) {
-    k2_bf16<<<p.k2_grid, k2m::THREADS, k2m::SMEM, st>>>(p.map_wo, p.map_e, p.map_v, X, scale, partial, vprime, status,
+    k2_bf16<<<p.k2_grid, k2m::THREADS, k2m::SMEM, st>>>(p.map_wo, p.map_e, p.map_v, p.map_x, scale, partial, vprime, status,
                                                         p.mt_per_grid * g.B, p.mt_per_grid, p.strips, p.k2_tiles, p.nbmax, g);
     return cudaGetLastError() == cudaSuccess ? 0 : -1;
 }

@@ -366,7 +366,8 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
     if (is_bf16(h)) {
         if ((rc = dev_alloc(h, &h->w1_bf16, sets * NH * 192 * 64))) return rc;
         if ((rc = dev_alloc(h, &h->wo_bf16, sets * NH * 64 * 64))) return rc;
-        if (bf16_setup(h->bf, h->w1_bf16, h->wo_bf16, (int)sets, (const __nv_bfloat16*)h->E, (const __nv_bfloat16*)h->V, g,
+        if (bf16_setup(h->bf, h->w1_bf16, h->wo_bf16, (int)sets, (const __nv_bfloat16*)h->E, (const __nv_bfloat16*)h->V,
+                       (const __nv_bfloat16*)h->X, g,
                        prop.multiProcessorCount) != 0)
             return fail(h, SLIME_CA_ECUDA, "tensor-map / kernel attribute set-up failed: " + std::string(bf16_error()));
     } else {
