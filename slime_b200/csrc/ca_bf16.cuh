@@ -53,14 +53,14 @@ struct Bf16Plan {
 
 // ---- shared-memory maps (byte offsets from a 1024-aligned base) -------------------------------------------
 namespace k1b {
-constexpr int A_X = 0;                                   // 2 x 16 KB: X operand of the current / next tile
-constexpr int A_CONV = 2 * 16384;                        // 4 x 16 KB: stencil operand slots, two per half
+constexpr int A_X = 0;                                   // 16 KB: X operand of the current tile
+constexpr int A_CONV = 16384;                            // 4 x 16 KB: stencil operand slots, two per half
 constexpr int W0 = A_CONV + 4 * 16384, W_STAGE = 24576;  // 2 x 24 KB: Wp|Wi|Wv rows of a head
 constexpr int STG_E = W0 + 2 * W_STAGE, STG_V = STG_E + 16384;   // staging tiles of the TMA stores
 constexpr int STG_COL_E = STG_V + 16384, STG_COL_V = STG_COL_E + 2048;   // last two columns  [8][2] cells
 constexpr int STG_ROW_E = STG_COL_V + 2048, STG_ROW_V = STG_ROW_E + 4096; // last two rows     [2][16] cells
 constexpr int STG_COR_E = STG_ROW_V + 4096, STG_COR_V = STG_COR_E + 1024; // their corner      [2][2] cells
-constexpr int XH = STG_COR_V + 1024, XH_BYTES = 10 * 18 * 128;   // state halo tile, plain [10][18] cells x 128 B
+constexpr int XH = STG_COR_V + 1024, XH_BYTES = 10 * 18 * 256;   // state halo tile, plain [10][18] cells x 64 fp32
 constexpr int PRM_ST = XH + XH_BYTES, PRM_EP = PRM_ST + NH * PRM * 4;   // per-tile copies of the head parameters
 constexpr int BARS = PRM_EP + NH * PRM * 4, TMEM_PTR = BARS + 24 * 8;
 constexpr int BYTES = TMEM_PTR + 16;
@@ -127,8 +127,8 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
     uint64_t* w_empty = bars + 3;       // [2] ... and was consumed                      (waits: TMA producer)
     uint64_t* ac_full = bars + 6;       // [4] stencil operand slot written              (waits: UMMA issuer)
     uint64_t* ac_empty = bars + 10;     // [4] ... and consumed                          (waits: the half that owns the slot)
-    uint64_t* ax_full = bars + 14;      // [2] X operand of a tile written               (waits: UMMA issuer)
-    uint64_t* ax_empty = bars + 16;     // [2] ... all 8 heads of that tile issued+done  (waits: stencil group)
+    uint64_t* ax_full = bars + 14;      // X operand of a tile written                   (waits: UMMA issuer)
+    uint64_t* ax_empty = bars + 16;     // ... all 8 heads of that tile issued+done      (waits: stencil group)
     uint64_t* tm_full = bars + 18;      // [2] accumulator buffer holds an item          (waits: epilogue group)
     uint64_t* tm_empty = bars + 20;     // [2] ... and was drained (256 arrivals)        (waits: UMMA issuer)
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(sm + k1b::TMEM_PTR);
@@ -170,18 +170,17 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
             const uint32_t idesc_u = ptx::umma_idesc_bf16(128, 64);
             const uint32_t idesc_iv = ptx::umma_idesc_bf16(128, 128);
             for (int k = 0; k < my_tiles; ++k) {
-                const int xb = k & 1;
                 for (int h = 0; h < NH; ++h) {
                     const int i = k * NH + h, ws = i & 1, half = h & 1, n = k * 4 + (h >> 1);
                     const int slot = half * 2 + (n & 1), tb = i & 1;
-                    if (h == 0) ptx::mbar_wait(&ax_full[xb], (k >> 1) & 1, status, 120);
+                    if (h == 0) ptx::mbar_wait(ax_full, k & 1, status, 120);
                     ptx::mbar_wait(&w_full[ws], (i >> 1) & 1, status, 121);
                     ptx::mbar_wait(&ac_full[slot], (n >> 1) & 1, status, 122);
                     ptx::mbar_wait(&tm_empty[tb], ((i >> 1) & 1) ^ 1, status, 123);
                     ptx::tc_fence_after();
                     const uint32_t wb = ptx::smem_u32(sm + k1b::W0 + ws * k1b::W_STAGE);
                     const uint64_t da = ptx::umma_desc_sw128(ptx::smem_u32(sm + k1b::A_CONV + slot * 16384));
-                    const uint64_t dx = ptx::umma_desc_sw128(ptx::smem_u32(sm + k1b::A_X + xb * 16384));
+                    const uint64_t dx = ptx::umma_desc_sw128(ptx::smem_u32(sm + k1b::A_X));
                     const uint64_t dwp = ptx::umma_desc_sw128(wb);
                     const uint64_t dwiv = ptx::umma_desc_sw128(wb + 64 * 128);
                     const uint32_t acc = tmem + tb * 192;
@@ -192,7 +191,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                     ptx::umma_commit(&w_empty[ws]);
                     ptx::umma_commit(&ac_empty[slot]);
                     ptx::umma_commit(&tm_full[tb]);
-                    if (h == NH - 1) ptx::umma_commit(&ax_empty[xb]);
+                    if (h == NH - 1) ptx::umma_commit(ax_empty);
                 }
             }
         }
@@ -204,9 +203,8 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
         for (int k = 0; k < my_tiles; ++k) {
             const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
             const int set = t.b / g.per_set;
-            uint8_t* a_x = sm + k1b::A_X + (k & 1) * 16384;
+            uint8_t* a_x = sm + k1b::A_X;
             ptx::bar_sync(1, 256);                                        // both halves are done with the last halo
-            ptx::mbar_wait(&ax_empty[k & 1], ((k >> 1) & 1) ^ 1, status, 130);
             const float* sc = scale + t.b * NC;
             if (tid < NH * PRM) prm_s[tid] = __ldg(prm + (size_t)set * NH * PRM + tid);
             if (k + 1 < my_tiles && tid < 180) {       // next tile's halo cells: one 128-byte line each, into L2
@@ -215,7 +213,8 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                 ptx::prefetch_l2(X + (size_t)tn.b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC);
             }
             {
-                // 180 cells x 8 chunks over 256 threads: issue every global load first, then scale and store
+                // 180 cells x 8 chunks over 256 threads: issue every global load first, then scale, round to bf16
+                // (the value both operands are made of) and store: fp32 to the halo tile, bf16 to the X operand
                 const int q = tid & 7;                 // constant per thread: 256 is a multiple of 8
                 const float4 s0 = __ldg(reinterpret_cast<const float4*>(sc + q * 8));
                 const float4 s1 = __ldg(reinterpret_cast<const float4*>(sc + q * 8 + 4));
@@ -228,6 +227,9 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                         raw[n] = *reinterpret_cast<const uint4*>(X + (size_t)t.b * xplane + ((size_t)g.xrow(r) * g.W + x) * NC + q * 8);
                     }
                 }
+                // the X operand is single-buffered: the last tile's products have long been issued by the time the
+                // loads above come back
+                ptx::mbar_wait(ax_empty, (k & 1) ^ 1, status, 130);
 #pragma unroll
                 for (int n = 0; n < 6; ++n) {
                     const int cell = (tid >> 3) + n * 32;
@@ -238,7 +240,10 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                         f[0] *= s0.x; f[1] *= s0.y; f[2] *= s0.z; f[3] *= s0.w;
                         f[4] *= s1.x; f[5] *= s1.y; f[6] *= s1.z; f[7] *= s1.w;
                         const uint4 v = pack8(f);
-                        *reinterpret_cast<uint4*>(xh + cell * 128 + q * 16) = v;
+                        unpack8(v, f);
+                        float4* dst = reinterpret_cast<float4*>(xh + cell * 256 + q * 32);
+                        dst[0] = make_float4(f[0], f[1], f[2], f[3]);
+                        dst[1] = make_float4(f[4], f[5], f[6], f[7]);
                         if (hy >= 1 && hy <= TBH && hx >= 1 && hx <= TBW)
                             *reinterpret_cast<uint4*>(a_x + swz((hy - 1) * TBW + hx - 1, q)) = v;
                     }
@@ -246,9 +251,11 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
             }
             ptx::fence_proxy_async();
             ptx::bar_sync(1, 256);
-            if (tid == 0) ptx::mbar_arrive(&ax_full[k & 1]);
+            if (tid == 0) ptx::mbar_arrive(ax_full);
 
-            const int q = st & 7, x = st >> 3;
+            // a thread owns two adjacent columns x 4 channels: a row of the halo is four 16-byte loads (cells
+            // 2p .. 2p+3), shared by the two outputs, and nothing is unpacked
+            const int c4 = st & 15, p2 = st >> 4;
             for (int h = half; h < NH; h += 2) {
                 const int n = k * 4 + (h >> 1), slot = half * 2 + (n & 1);
                 uint8_t* a_conv = sm + k1b::A_CONV + slot * 16384;
@@ -257,33 +264,41 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                 for (int tt = 0; tt < 9; ++tt) { const float kv = prm_s[h * PRM + tt]; kt[tt] = ptx::make_f2(kv, kv); }
                 ptx::mbar_wait(&ac_empty[slot], ((n >> 1) & 1) ^ 1, status, 131);
                 // input row j feeds output rows j (tap row 0), j-1 (tap row 1) and j-2 (tap row 2)
-                ptx::f2 s1[4], s2[4];
+                ptx::f2 s1[2][2], s2[2][2];
 #pragma unroll
                 for (int j = 0; j < 10; ++j) {
-                    const uint8_t* row = xh + (j * 18 + x) * 128 + q * 16;
-                    ptx::f2 c0[4], c1[4], c2[4], nw[4], md[4];
-                    unpack8p(*reinterpret_cast<const uint4*>(row), c0);
-                    unpack8p(*reinterpret_cast<const uint4*>(row + 128), c1);
-                    unpack8p(*reinterpret_cast<const uint4*>(row + 256), c2);
-                    if (j >= 2) {
-                        ptx::f2 o[4];
+                    const uint8_t* row = xh + (j * 18 + 2 * p2) * 256 + c4 * 16;
+                    ptx::f2 c[4][2];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            o[e] = ptx::fma2(kt[6], c0[e], ptx::fma2(kt[7], c1[e], ptx::fma2(kt[8], c2[e], s2[e])));
-                        *reinterpret_cast<uint4*>(a_conv + swz((j - 2) * TBW + x, q)) = pack8p(o);
-                    }
-                    if (j >= 1 && j <= 8) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            md[e] = ptx::fma2(kt[3], c0[e], ptx::fma2(kt[4], c1[e], ptx::fma2(kt[5], c2[e], s1[e])));
-                    }
-                    if (j <= 7) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            nw[e] = ptx::fma2(kt[0], c0[e], ptx::fma2(kt[1], c1[e], ptx::mul2(kt[2], c2[e])));
+                    for (int i = 0; i < 4; ++i) {
+                        const float4 w = *reinterpret_cast<const float4*>(row + i * 256);
+                        c[i][0] = ptx::make_f2(w.x, w.y);
+                        c[i][1] = ptx::make_f2(w.z, w.w);
                     }
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) { s2[e] = md[e]; s1[e] = nw[e]; }
+                    for (int col = 0; col < 2; ++col) {
+                        ptx::f2 nw[2], md[2];
+                        if (j >= 2) {
+                            ptx::f2 o[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e)
+                                o[e] = ptx::fma2(kt[6], c[col][e], ptx::fma2(kt[7], c[col + 1][e], ptx::fma2(kt[8], c[col + 2][e], s2[col][e])));
+                            *reinterpret_cast<uint2*>(a_conv + swz((j - 2) * TBW + 2 * p2 + col, c4 >> 1) + (c4 & 1) * 8) =
+                                make_uint2(ptx::f2_to_bf16x2(o[0]), ptx::f2_to_bf16x2(o[1]));
+                        }
+                        if (j >= 1 && j <= 8) {
+#pragma unroll
+                            for (int e = 0; e < 2; ++e)
+                                md[e] = ptx::fma2(kt[3], c[col][e], ptx::fma2(kt[4], c[col + 1][e], ptx::fma2(kt[5], c[col + 2][e], s1[col][e])));
+                        }
+                        if (j <= 7) {
+#pragma unroll
+                            for (int e = 0; e < 2; ++e)
+                                nw[e] = ptx::fma2(kt[0], c[col][e], ptx::fma2(kt[1], c[col + 1][e], ptx::mul2(kt[2], c[col + 2][e])));
+                        }
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) { s2[col][e] = md[e]; s1[col][e] = nw[e]; }
+                    }
                 }
                 ptx::fence_proxy_async();
                 ptx::bar_sync(2 + half, 128);
@@ -332,6 +347,10 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                 const int i = k * NH + h, tb = i & 1;
                 const float mus = prm_e[h * PRM + 9];            // mu * s; Wp carries s and Wi carries log2(e)
                 const ptx::f2 neg_mus2 = ptx::make_f2(-mus, -mus), two2 = ptx::make_f2(2.f, 2.f), minus_one2 = ptx::make_f2(-1.f, -1.f);
+                // clamp(G*I) before the exponential = clamp of the rounded exponential (rounding to bf16 is monotone):
+                // two packed bf16 min/max per pair instead of four fp32 ones
+                const uint32_t e_max = pack_bf16(ptx::ex2(ACT_CLAMP * LOG2E), ptx::ex2(ACT_CLAMP * LOG2E));
+                const uint32_t e_min = pack_bf16(ptx::ex2(-ACT_CLAMP * LOG2E), ptx::ex2(-ACT_CLAMP * LOG2E));
                 ptx::mbar_wait(&tm_full[tb], (i >> 1) & 1, status, 140);
                 ptx::tc_fence_after();
                 const uint32_t t_lane = tmem + ((uint32_t)(quad * 32) << 16) + tb * 192;
@@ -353,8 +372,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                         const ptx::f2 gr = ptx::fma2(ptx::make_f2(ptx::ex2(-q0), ptx::ex2(-q1)), two2, minus_one2);
                         float a0, a1;
                         ptx::split_f2(ptx::mul2(gr, ptx::make_f2(__uint_as_float(ri[2 * j]), __uint_as_float(ri[2 * j + 1]))), a0, a1);
-                        pe[sub][j] = pack_bf16(ptx::ex2(fminf(fmaxf(a0, -ACT_CLAMP * LOG2E), ACT_CLAMP * LOG2E)),
-                                               ptx::ex2(fminf(fmaxf(a1, -ACT_CLAMP * LOG2E), ACT_CLAMP * LOG2E)));
+                        pe[sub][j] = ptx::max_bf16x2(ptx::min_bf16x2(pack_bf16(ptx::ex2(a0), ptx::ex2(a1)), e_max), e_min);
                         pv[sub][j] = pack_bf16(__uint_as_float(rv[2 * j]), __uint_as_float(rv[2 * j + 1]));
                     }
                 }

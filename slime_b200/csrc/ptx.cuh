@@ -201,6 +201,8 @@ __device__ __forceinline__ uint32_t f2_to_bf16x2(f2 a) {
 }
 
 // ---- math ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t min_bf16x2(uint32_t a, uint32_t b) { uint32_t r; asm("min.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r; }
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) { uint32_t r; asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b)); return r; }
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
