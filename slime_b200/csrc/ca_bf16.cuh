@@ -582,12 +582,13 @@ __device__ __forceinline__ void k2_epilogue(const CaTile& t, uint32_t acc_taddr,
 //   warps 8-15   B: V' = E * box3(R) -> one of two swizzled A operand tiles (every thread arrives on the operand's
 //                mbarrier), then releases the stage
 //   warp 16      TMA producer: per (macro tile, head) the head's Wo slice (double-buffered), per block E and V
-//   warp 17      UMMA issuer: Y[tile] += V'_h Wo_h, heads in order          (warp 18 has no role)
+//   warp 17      UMMA issuer: Y[tile] += V'_h Wo_h, heads in order
+//   warp 18      TMA producer of the epilogues' state tiles (a wait for a free buffer never holds back E / V)
 // so that each of the SM's four schedulers (warp index mod 4) carries two A warps and two B warps, the half-filled
-// ninth A warp sits alone on the fourth, and the two single-thread roles on the first two.
+// ninth A warp sits alone on the fourth, and the three single-thread roles on the first three.
 // The epilogue of a macro tile (X+ = scale X + dt Y, channel sums) is interleaved into the first head of the next one:
 // A's first eight warps drain the even accumulators, B the odd ones, each just before its own block of that tile.  The
-// tile's state comes to the draining set by TMA (each set owns one 16 KB buffer, loaded one block ahead) and X+ leaves
+// tile's state comes to the draining set by TMA (each set owns one 16 KB buffer, refilled as soon as it is free) and X+ leaves
 // by a TMA store from the same buffer.
 // Every cell's arithmetic is the same sequence of operations wherever the cell sits in a tile or a block, so shifting a
 // torus shifts the result bit for bit.
@@ -698,18 +699,6 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
         // ================= TMA producer ===================================================================
         if (lane == 0) {
             uint32_t it = 0, wit = 0;       // blocks and heads so far
-            uint32_t nx[2] = {0, 0};        // state tiles loaded for set A (even tiles) and set B (odd tiles)
-            MacroTile prev;
-            prev.nb = 0;
-            prev.b = prev.mx0 = prev.my0 = prev.tile0 = 0;
-            // the state of tile b of macro tile `mt` for the epilogue that drains it, into the draining set's buffer
-            auto load_x = [&](const MacroTile& mt, int b) {
-                const int xb = b & 1;
-                ptx::mbar_wait(&x_empty[xb], (nx[xb] & 1) ^ 1, status, 212);
-                ptx::mbar_expect_tx(&x_full[xb], 16384);
-                ptx::tma_load_4d(sm + k2m::XT + xb * 16384, &map_x, 0, mt.mx0, g.hx + mt.my0 + b * k2m::BR, mt.b, &x_full[xb]);
-                ++nx[xb];
-            };
             for (int k = 0; k < my_mt; ++k) {
                 const MacroTile m = macro_tile(blockIdx.x + k * gridDim.x, mt_per_grid, strips, g.H, nbmax);
                 const int set = m.b / g.per_set;
@@ -728,15 +717,27 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
                         // outside the tensor read as zero and only feed values nobody uses)
                         ptx::tma_load_4d(st, &map_e, 0, m.mx0, m.my0 + 4 * b + 4, plane, &full[s]);
                         ptx::tma_load_4d(st + k2m::E_BYTES, &map_v, 0, m.mx0 + 1, m.my0 + 4 * b + 3, plane, &full[s]);
-                        // tile b+1 of the macro tile before is drained ahead of block b+1 of this head: its state now
-                        if (h == 0 && b + 1 < prev.nb && b + 1 < m.nb) load_x(prev, b + 1);
                     }
-                    if (h == 0)
-                        for (int b = m.nb; b < prev.nb; ++b) load_x(prev, b);       // tiles this macro tile does not reach
                 }
-                prev = m;
             }
-            for (int b = 0; b < prev.nb; ++b) load_x(prev, b);                      // the last macro tile's
+        }
+    } else if (warp == 18) {
+        // ================= TMA producer of the epilogues' state tiles ==========================================
+        // Tile b of a macro tile is drained by set A (even b) or B (odd b), in this order, while the next macro tile
+        // runs its first head; its state goes into that set's buffer as soon as the buffer is free.  A producer of
+        // its own, so that a wait for a buffer never holds back the E / V blocks.
+        if (lane == 0) {
+            uint32_t nx[2] = {0, 0};        // state tiles loaded for set A and set B
+            for (int k = 0; k < my_mt; ++k) {
+                const MacroTile m = macro_tile(blockIdx.x + k * gridDim.x, mt_per_grid, strips, g.H, nbmax);
+                for (int b = 0; b < m.nb; ++b) {
+                    const int xb = b & 1;
+                    ptx::mbar_wait(&x_empty[xb], (nx[xb] & 1) ^ 1, status, 212);
+                    ptx::mbar_expect_tx(&x_full[xb], 16384);
+                    ptx::tma_load_4d(sm + k2m::XT + xb * 16384, &map_x, 0, m.mx0, g.hx + m.my0 + b * k2m::BR, m.b, &x_full[xb]);
+                    ++nx[xb];
+                }
+            }
         }
     } else if (warp == 17) {
         // ================= UMMA issuer ====================================================================
@@ -766,7 +767,7 @@ k2_bf16(const __grid_constant__ CUtensorMap map_wo, const __grid_constant__ CUte
                 acc_par ^= (1u << m.nb) - 1u;
             }
         }
-    } else if (warp != 18) {
+    } else {
         // ================= the two box-sum sets ==================================================================
         const bool is_a = warp < 8 || warp == 19;
         const int gt = warp == 19 ? 256 + lane : (is_a ? tid : tid - 256);     // thread within its set
