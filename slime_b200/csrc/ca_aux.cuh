@@ -56,16 +56,49 @@ k_reduce_partials(const float* __restrict__ partial, int n_partials, double* __r
     if (sub == 0) seg_sums[((size_t)b * nseg + blockIdx.x) * NC + c] = (red[0][c] + red[1][c]) + (red[2][c] + red[3][c]);
 }
 
-// Stage 2: sums[b][c] = sum of the segments (fixed order).  mode 0: leave it there; 1: also set mass = sums
-// and scale = 1 (a freshly loaded state); 2: also scale = mass / sums (after a step).
-__global__ void k_finish_sums(const double* __restrict__ seg_sums, int nseg, double* __restrict__ sums,
-                              double* __restrict__ mass, float* __restrict__ scale, int mode) {
-    const int b = blockIdx.x, c = threadIdx.x;
+// Both stages of the cross-tile reduction in one launch: segment s of grid b sums its share of the partials in fp64
+// (as k_reduce_partials), and the block that finishes last for its grid (a ticket per grid, handed back at zero) adds
+// the segments in their fixed order, so the result does not depend on which block that is.
+// mode 0: sums only; 1: also mass = sums and scale = 1 (a freshly loaded state); 2: also scale = mass / sums.
+__global__ void __launch_bounds__(256)
+k_reduce_finish(const float* __restrict__ partial, int n_partials, double* __restrict__ seg_sums, size_t lo_offset,
+                int* __restrict__ tickets, double* __restrict__ sums, double* __restrict__ mass,
+                float* __restrict__ scale, int mode) {
+    __shared__ double red[4][64];
+    __shared__ int is_last;
+    const int b = blockIdx.y, c = threadIdx.x & 63, sub = threadIdx.x >> 6;
+    const int nseg = gridDim.x;
+    const int per_seg = (n_partials + nseg - 1) / nseg;
+    const int per_sub = (per_seg + 3) / 4;
+    const int lo = blockIdx.x * per_seg + sub * per_sub;
+    int hi = lo + per_sub;
+    const int seg_hi = min((blockIdx.x + 1) * per_seg, n_partials);
+    if (hi > seg_hi) hi = seg_hi;
     double s = 0.0;
-    for (int i = 0; i < nseg; ++i) s += seg_sums[((size_t)b * nseg + i) * NC + c];
-    sums[b * NC + c] = s;
-    if (mode == 1) { mass[b * NC + c] = s; scale[b * NC + c] = 1.f; }
-    if (mode == 2) scale[b * NC + c] = (float)(mass[b * NC + c] / s);
+    for (int t = lo; t < hi; ++t) {
+        const size_t o = ((size_t)b * n_partials + t) * NC + c;
+        s += (double)partial[o];
+        if (lo_offset) s += (double)partial[o + lo_offset];
+    }
+    red[sub][c] = s;
+    __syncthreads();
+    if (sub == 0) {
+        seg_sums[((size_t)b * nseg + blockIdx.x) * NC + c] = (red[0][c] + red[1][c]) + (red[2][c] + red[3][c]);
+        __threadfence();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(&tickets[b], 1) == nseg - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (sub == 0) {
+        double t = 0.0;
+        for (int i = 0; i < nseg; ++i) t += __ldcg(&seg_sums[((size_t)b * nseg + i) * NC + c]);
+        sums[b * NC + c] = t;
+        if (mode == 1) { mass[b * NC + c] = t; scale[b * NC + c] = 1.f; }
+        if (mode == 2) scale[b * NC + c] = (float)(mass[b * NC + c] / t);
+    }
+    if (threadIdx.x == 0) tickets[b] = 0;
 }
 
 // scale = mass / sums from buffers the caller may have all-reduced.

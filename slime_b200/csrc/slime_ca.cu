@@ -41,6 +41,7 @@ struct slime_ca {
     int partial_cap = 0;
     size_t partial_lo = 0;          // fp32 path: offset (floats) of the remainders of the step's tile sums
     double* seg_sums = nullptr;
+    int* tickets = nullptr;          // one per grid: blocks of the reduction that have finished (back at 0 after each launch)
     int k1_tiles = 0, k2_tiles = 0, tiles_x = 0;
     // weights
     float* wpiv_f32 = nullptr;      // [sets][8][64][192]  rows c_in, columns Wp | Wi | Wv
@@ -128,16 +129,16 @@ int channel_sums(slime_ca* h, int mode, cudaStream_t st) {
     else k_channel_partials<float><<<grid, 256, 0, st>>>((const float*)h->X, h->partial, h->g);
     LAUNCHED(h);
     const int nseg = chunks < 64 ? chunks : 64;
-    k_reduce_partials<<<dim3(nseg, h->g.B), 256, 0, st>>>(h->partial, chunks, h->seg_sums);
-    LAUNCHED(h);
-    k_finish_sums<<<h->g.B, 64, 0, st>>>(h->seg_sums, nseg, h->sums, h->mass, h->scale, mode);
+    k_reduce_finish<<<dim3(nseg, h->g.B), 256, 0, st>>>(h->partial, chunks, h->seg_sums, 0, h->tickets, h->sums, h->mass,
+                                                        h->scale, mode);
     LAUNCHED(h);
     return SLIME_CA_OK;
 }
 
 // the kernels of one step up to and including BUF_SUMS; `emit` = V' destination or null
-// `ev`, when given, receives three records: before k1, between k1 and k2, after k2
-int step_kernels(slime_ca* h, void* emit, cudaStream_t st, cudaEvent_t* ev = nullptr) {
+// `ev`, when given, receives three records: before k1, between k1 and k2, after k2.  sums_mode 2 also sets the new
+// scale from the local sums (a caller that all-reduces the sums first passes 0 and sets the scale afterwards)
+int step_kernels(slime_ca* h, void* emit, cudaStream_t st, cudaEvent_t* ev = nullptr, int sums_mode = 0) {
     const Geom& g = h->g;
     if (ev) CK(h, cudaEventRecord(ev[0], st));
     if (is_bf16(h)) {
@@ -161,9 +162,8 @@ int step_kernels(slime_ca* h, void* emit, cudaStream_t st, cudaEvent_t* ev = nul
     }
     if (ev) CK(h, cudaEventRecord(ev[2], st));
     const int nseg = h->k2_tiles < 64 ? h->k2_tiles : 64;
-    k_reduce_partials<<<dim3(nseg, g.B), 256, 0, st>>>(h->partial, h->k2_tiles, h->seg_sums, is_bf16(h) ? 0 : h->partial_lo);
-    LAUNCHED(h);
-    k_finish_sums<<<g.B, 64, 0, st>>>(h->seg_sums, nseg, h->sums, h->mass, h->scale, 0);
+    k_reduce_finish<<<dim3(nseg, g.B), 256, 0, st>>>(h->partial, h->k2_tiles, h->seg_sums, is_bf16(h) ? 0 : h->partial_lo,
+                                                     h->tickets, h->sums, h->mass, h->scale, sums_mode);
     LAUNCHED(h);
     return SLIME_CA_OK;
 }
@@ -352,6 +352,8 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
     h->partial_lo = is_bf16(h) ? 0 : (size_t)g.B * h->partial_cap * NC;
     if ((rc = dev_alloc(h, &h->partial, (size_t)g.B * h->partial_cap * NC + h->partial_lo))) return rc;
     if ((rc = dev_alloc(h, &h->seg_sums, (size_t)g.B * 64 * NC))) return rc;
+    if ((rc = dev_alloc(h, &h->tickets, (size_t)g.B))) return rc;
+    CK(h, cudaMemset(h->tickets, 0, (size_t)g.B * sizeof(int)));
     if ((rc = dev_alloc(h, &h->dev_status, 1))) return rc;
     CK(h, cudaMemset(h->dev_status, 0, sizeof(int)));
     CK(h, cudaHostAlloc((void**)&h->host_status, sizeof(int), cudaHostAllocDefault));
@@ -382,7 +384,7 @@ int slime_ca_create(const slime_ca_config* cfg, slime_ca** out) {
 int slime_ca_destroy(slime_ca* h) {
     if (!h) return SLIME_CA_EINVAL;
     cudaSetDevice(h->cfg.device);
-    void* ptrs[] = {h->X, h->E, h->V, h->vprime[0], h->vprime[1], h->scale, h->mass, h->sums, h->partial, h->seg_sums,
+    void* ptrs[] = {h->X, h->E, h->V, h->vprime[0], h->vprime[1], h->scale, h->mass, h->sums, h->partial, h->seg_sums, h->tickets,
                     h->wpiv_f32, h->wo_f32, h->prm, h->w1_bf16, h->wo_bf16, h->gram_part, h->head_rank,
                     h->pearson_part, h->fit_dev, h->dev_status, h->master, h->set_stats, h->parent, h->evolve_info};
     for (void* p : ptrs)
@@ -546,14 +548,11 @@ int slime_ca_step(slime_ca* h, int n_steps, void* stream) {
     CK(h, cudaSetDevice(h->cfg.device));
     cudaStream_t st = (cudaStream_t)stream;
     if ((rc = poll_status(h, st))) return rc;
-    const int n = h->g.B * NC;
     for (int i = 0; i < n_steps; ++i) {
         void* emit = nullptr;
         if (h->cfg.keep_vprime && i >= n_steps - 2) { h->vp_last ^= 1; emit = h->vprime[h->vp_last]; ++h->vp_steps; h->fitness_valid = false; }
-        rc = step_kernels(h, emit, st);
+        rc = step_kernels(h, emit, st, nullptr, 2);
         if (rc) return rc;
-        k_scale_from_sums<<<(n + 255) / 256, 256, 0, st>>>(h->sums, h->mass, h->scale, n);
-        LAUNCHED(h);
         ++h->steps_done;
     }
     return n_steps > 0 ? publish_status(h, st) : SLIME_CA_OK;
@@ -572,13 +571,10 @@ int slime_ca_step_timed(slime_ca* h, int n_steps, void* stream, float* ms) {
     evs.v.assign((size_t)n_steps * 4, nullptr);
     std::vector<cudaEvent_t>& ev = evs.v;
     for (auto& e : ev) CK(h, cudaEventCreate(&e));
-    const int n = h->g.B * NC;
     h->vp_steps = 0; h->fitness_valid = false;      // these steps do not emit V': the kept pair no longer matches the state
     for (int i = 0; i < n_steps; ++i) {
-        rc = step_kernels(h, nullptr, st, &ev[(size_t)i * 4]);
+        rc = step_kernels(h, nullptr, st, &ev[(size_t)i * 4], 2);
         if (rc) return rc;
-        k_scale_from_sums<<<(n + 255) / 256, 256, 0, st>>>(h->sums, h->mass, h->scale, n);
-        LAUNCHED(h);
         CK(h, cudaEventRecord(ev[(size_t)i * 4 + 3], st));
         ++h->steps_done;
     }
