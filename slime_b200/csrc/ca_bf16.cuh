@@ -61,12 +61,12 @@ constexpr int STG_COL_E = STG_V + 16384, STG_COL_V = STG_COL_E + 2048;   // last
 constexpr int STG_ROW_E = STG_COL_V + 2048, STG_ROW_V = STG_ROW_E + 4096; // last two rows     [2][16] cells
 constexpr int STG_COR_E = STG_ROW_V + 4096, STG_COR_V = STG_COR_E + 1024; // their corner      [2][2] cells
 constexpr int XH = STG_COR_V + 1024, XH_BYTES = 10 * 18 * 256;   // state halo tile, plain [10][18] cells x 64 fp32
-constexpr int PRM_ST = XH + XH_BYTES, PRM_EP = PRM_ST + NH * PRM * 4;   // per-tile copies of the head parameters
-constexpr int BARS = PRM_EP + NH * PRM * 4, TMEM_PTR = BARS + 24 * 8;
+constexpr int PRM_ST = XH + XH_BYTES;                    // per-tile copy of the head parameters (stencil taps)
+constexpr int BARS = PRM_ST + NH * PRM * 4, TMEM_PTR = BARS + 24 * 8;
 constexpr int BYTES = TMEM_PTR + 16;
 constexpr int SMEM = BYTES + 1024;    // slack for manual 1024-byte alignment
 constexpr uint32_t TMEM_COLS = 512;   // two accumulator buffers of 192 columns
-constexpr int THREADS = 576;
+constexpr int THREADS = 608;
 static_assert(SMEM <= 227 * 1024, "k1 shared memory");
 }  // namespace k1b
 
@@ -103,13 +103,15 @@ __device__ __forceinline__ CaTile ca_tile(int t, int tiles_per_grid, int tiles_x
     return r;
 }
 
-// k1: persistent, warp-specialised, one CTA per SM (576 threads):
+// k1: persistent, warp-specialised, one CTA per SM (608 threads):
 //   warps 0-7   stencil group: loads the tile's state halo (scale applied) and the X operand, then its two
 //               4-warp halves take alternate heads: 3x3 stencil marching down columns in packed fp32 -> A operand
-//   warps 8-15  epilogue group: TMEM -> growth bell, E = exp(G*I) -> swizzled staging tiles -> TMA store of the
-//               whole tile (+ register stores of the apron duplicates of edge cells)
+//   warps 8-15  epilogue group: TMEM -> growth bell, E = exp(G*I) -> swizzled staging tiles (+ register stores of
+//               the apron duplicates of edge cells on ragged grids)
 //   warp 16     TMA producer of the per-head weight tiles (2-stage ring)
 //   warp 17     UMMA issuer: U (N=64) and I|V (N=128) into a double-buffered 192-column TMEM accumulator
+//   warp 18     store warp: issues the TMA stores of every finished item, so that the epilogue group never meets at
+//               a barrier (its threads arrive on an mbarrier when their staging is written and move on)
 // ALIGNED: the grid is made of whole tiles (W a multiple of 16, and H a multiple of 8 on a torus), so the wrapped
 // copies of edge cells are whole pieces of a tile and go out as extra TMA stores; otherwise the threads that own
 // edge cells store the copies from registers.
@@ -131,6 +133,8 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
     uint64_t* ax_empty = bars + 16;     // ... all 8 heads of that tile issued+done      (waits: stencil group)
     uint64_t* tm_full = bars + 18;      // [2] accumulator buffer holds an item          (waits: epilogue group)
     uint64_t* tm_empty = bars + 20;     // [2] ... and was drained (256 arrivals)        (waits: UMMA issuer)
+    uint64_t* stg_full = bars + 22;     // staging tiles of an item written (256 arrivals) (waits: store warp)
+    uint64_t* stg_free = bars + 23;     // ... and read by the item's TMA stores         (waits: epilogue group)
     uint32_t* tmem_ptr = reinterpret_cast<uint32_t*>(sm + k1b::TMEM_PTR);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -138,6 +142,8 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
         for (int i = 0; i < 20; ++i) ptx::mbar_init(&bars[i], 1);
         ptx::mbar_init(&tm_empty[0], 256);
         ptx::mbar_init(&tm_empty[1], 256);
+        ptx::mbar_init(stg_full, 256);
+        ptx::mbar_init(stg_free, 1);
         ptx::fence_barrier_init();
         ptx::prefetch_tmap(&map_w1); ptx::prefetch_tmap(&sm_maps.e); ptx::prefetch_tmap(&sm_maps.v);
     }
@@ -194,6 +200,59 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                     if (h == NH - 1) ptx::umma_commit(ax_empty);
                 }
             }
+        }
+    } else if (warp == 18) {
+        // ================= store warp: the TMA stores of every finished item ==================================
+        // The epilogue group never meets at a barrier: its threads arrive on stg_full when their part of the staging
+        // tiles is written and go on to the next item; this thread issues the item's stores and hands the staging
+        // back (stg_free) as soon as the stores have read it.
+        if (lane == 0) {
+            for (int k = 0; k < my_tiles; ++k) {
+                const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
+                // whole-tile grids: which sides of the grid this tile touches
+                const bool left = t.tx0 == 0, right = t.tx0 + TBW == g.W;
+                const bool top = g.wrap_y && t.ty0 == 0, bottom = g.wrap_y && t.ty0 + TBH == g.H;
+                for (int h = 0; h < NH; ++h) {
+                    const int i = k * NH + h;
+                    ptx::mbar_wait(stg_full, i & 1, status, 150);
+                    const int px = t.tx0 + APRON, py = t.ty0 + APRON, pl = t.b * NH + h;
+                    ptx::tma_store_4d(&sm_maps.e, sm + k1b::STG_E, 0, px, py, pl);
+                    ptx::tma_store_4d(&sm_maps.v, sm + k1b::STG_V, 0, px, py, pl);
+                    if (ALIGNED) {
+                        // wrapped copies: pieces that land at the high end of an apron are the whole tile stored at the
+                        // shifted position (all but the first two columns / rows are clipped); pieces that land at
+                        // the low end come from the small staging tiles
+                        const int hx = g.W + APRON, hy = g.H + APRON;
+                        if (left) { ptx::tma_store_4d(&sm_maps.e, sm + k1b::STG_E, 0, hx, py, pl); ptx::tma_store_4d(&sm_maps.v, sm + k1b::STG_V, 0, hx, py, pl); }
+                        if (top) { ptx::tma_store_4d(&sm_maps.e, sm + k1b::STG_E, 0, px, hy, pl); ptx::tma_store_4d(&sm_maps.v, sm + k1b::STG_V, 0, px, hy, pl); }
+                        if (left && top) { ptx::tma_store_4d(&sm_maps.e, sm + k1b::STG_E, 0, hx, hy, pl); ptx::tma_store_4d(&sm_maps.v, sm + k1b::STG_V, 0, hx, hy, pl); }
+                        if (right) {
+                            ptx::tma_store_4d(&sm_maps.e_col, sm + k1b::STG_COL_E, 0, 0, py, pl);
+                            ptx::tma_store_4d(&sm_maps.v_col, sm + k1b::STG_COL_V, 0, 0, py, pl);
+                            if (top) {
+                                ptx::tma_store_4d(&sm_maps.e_col, sm + k1b::STG_COL_E, 0, 0, hy, pl);
+                                ptx::tma_store_4d(&sm_maps.v_col, sm + k1b::STG_COL_V, 0, 0, hy, pl);
+                            }
+                        }
+                        if (bottom) {
+                            ptx::tma_store_4d(&sm_maps.e_row, sm + k1b::STG_ROW_E, 0, px, 0, pl);
+                            ptx::tma_store_4d(&sm_maps.v_row, sm + k1b::STG_ROW_V, 0, px, 0, pl);
+                            if (left) {
+                                ptx::tma_store_4d(&sm_maps.e_row, sm + k1b::STG_ROW_E, 0, hx, 0, pl);
+                                ptx::tma_store_4d(&sm_maps.v_row, sm + k1b::STG_ROW_V, 0, hx, 0, pl);
+                            }
+                            if (right) {
+                                ptx::tma_store_4d(&sm_maps.e_cor, sm + k1b::STG_COR_E, 0, 0, 0, pl);
+                                ptx::tma_store_4d(&sm_maps.v_cor, sm + k1b::STG_COR_V, 0, 0, 0, pl);
+                            }
+                        }
+                    }
+                    ptx::bulk_commit();
+                    ptx::bulk_wait_read0();
+                    ptx::mbar_arrive(stg_free);
+                }
+            }
+            ptx::bulk_wait0();
         }
     } else if (warp < 8) {
         // ================= stencil group ======================================================================
@@ -307,26 +366,21 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
         }
     } else {
         // ================= epilogue group (warps 8..15) ========================================================
-        const int et = tid - 256, quad = warp & 3, half = (warp - 8) >> 2;
+        const int quad = warp & 3, half = (warp - 8) >> 2;
         const int m_ep = quad * 32 + lane;                 // TMEM lane = cell of the tile this thread finishes
         uint8_t* stg_e = sm + k1b::STG_E;
         uint8_t* stg_v = sm + k1b::STG_V;
-        float* prm_e = reinterpret_cast<float*>(sm + k1b::PRM_EP);
         const bool tiny = g.W < 2 * APRON || (g.wrap_y && g.H < 2 * APRON);
         for (int k = 0; k < my_tiles; ++k) {
             const CaTile t = ca_tile(blockIdx.x + k * gridDim.x, tiles_per_grid, g.tiles_x, -g.he);
             const int set = t.b / g.per_set;
             const int r_ep = t.ty0 + (m_ep >> 4), x_ep = t.tx0 + (m_ep & 15);
             const bool valid_ep = r_ep < g.H + g.he && x_ep < g.W;
-            ptx::bar_sync(4, 256);                     // everyone is done with the last tile's parameters
-            if (et < NH * PRM) prm_e[et] = __ldg(prm + (size_t)set * NH * PRM + et);
-            ptx::bar_sync(4, 256);
-            // Apron positions that wrap onto this thread's cell (the TMA store below covers the cell itself and
-            // whatever hangs over the far edge).
+            // Apron positions that wrap onto this thread's cell (the store warp's TMA store covers the cell itself
+            // and whatever hangs over the far edge).
             const int cy = m_ep >> 4, cx = m_ep & 15;
-            // whole-tile grids: which sides of the grid this tile touches (uniform over the tile)
-            const bool left = t.tx0 == 0, right = t.tx0 + TBW == g.W;
-            const bool top = g.wrap_y && t.ty0 == 0, bottom = g.wrap_y && t.ty0 + TBH == g.H;
+            // whole-tile grids: does this tile touch the right / bottom side of the grid (uniform over the tile)
+            const bool right = t.tx0 + TBW == g.W, bottom = g.wrap_y && t.ty0 + TBH == g.H;
             const bool in_col = right && cx >= TBW - APRON, in_row = bottom && cy >= TBH - APRON;
             // ragged or tiny grids: per-thread targets (named registers, not an indexed array: an array would live
             // in local memory and put a load in front of every duplicate store).  Grids narrower or shorter than
@@ -345,7 +399,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
             const bool any_dup = !ALIGNED && valid_ep && (dup_x || dup_y || tiny);
             for (int h = 0; h < NH; ++h) {
                 const int i = k * NH + h, tb = i & 1;
-                const float mus = prm_e[h * PRM + 9];            // mu * s; Wp carries s and Wi carries log2(e)
+                const float mus = __ldg(prm + ((size_t)set * NH + h) * PRM + 9);   // mu * s; Wp carries s and Wi carries log2(e)
                 const ptx::f2 neg_mus2 = ptx::make_f2(-mus, -mus), two2 = ptx::make_f2(2.f, 2.f), minus_one2 = ptx::make_f2(-1.f, -1.f);
                 // clamp(G*I) before the exponential = clamp of the rounded exponential (rounding to bf16 is monotone):
                 // two packed bf16 min/max per pair instead of four fp32 ones
@@ -378,8 +432,7 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                 }
                 ptx::tc_fence_before();
                 ptx::mbar_arrive(&tm_empty[tb]);                  // the accumulator buffer is free again
-                if (et == 0) ptx::bulk_wait_read0();              // the last TMA stores are done reading the staging
-                ptx::bar_sync(4, 256);
+                ptx::mbar_wait(stg_free, (i & 1) ^ 1, status, 141);   // the last item's TMA stores are done reading the staging
 #pragma unroll
                 for (int sub = 0; sub < 2; ++sub) {
                     const int qa = half * 4 + sub * 2;
@@ -448,45 +501,9 @@ k1_bf16(const __grid_constant__ CUtensorMap map_w1, const __grid_constant__ K1St
                     }
                 }
                 ptx::fence_proxy_async();
-                ptx::bar_sync(4, 256);
-                if (et == 0) {
-                    const int px = t.tx0 + APRON, py = t.ty0 + APRON, pl = t.b * NH + h;
-                    ptx::tma_store_4d(&sm_maps.e, stg_e, 0, px, py, pl);
-                    ptx::tma_store_4d(&sm_maps.v, stg_v, 0, px, py, pl);
-                    if (ALIGNED) {
-                        // wrapped copies: pieces that land at the high end of an apron are the whole tile stored at the
-                        // shifted position (all but the first two columns / rows are clipped); pieces that land at
-                        // the low end come from the small staging tiles
-                        const int hx = g.W + APRON, hy = g.H + APRON;
-                        if (left) { ptx::tma_store_4d(&sm_maps.e, stg_e, 0, hx, py, pl); ptx::tma_store_4d(&sm_maps.v, stg_v, 0, hx, py, pl); }
-                        if (top) { ptx::tma_store_4d(&sm_maps.e, stg_e, 0, px, hy, pl); ptx::tma_store_4d(&sm_maps.v, stg_v, 0, px, hy, pl); }
-                        if (left && top) { ptx::tma_store_4d(&sm_maps.e, stg_e, 0, hx, hy, pl); ptx::tma_store_4d(&sm_maps.v, stg_v, 0, hx, hy, pl); }
-                        if (right) {
-                            ptx::tma_store_4d(&sm_maps.e_col, sm + k1b::STG_COL_E, 0, 0, py, pl);
-                            ptx::tma_store_4d(&sm_maps.v_col, sm + k1b::STG_COL_V, 0, 0, py, pl);
-                            if (top) {
-                                ptx::tma_store_4d(&sm_maps.e_col, sm + k1b::STG_COL_E, 0, 0, hy, pl);
-                                ptx::tma_store_4d(&sm_maps.v_col, sm + k1b::STG_COL_V, 0, 0, hy, pl);
-                            }
-                        }
-                        if (bottom) {
-                            ptx::tma_store_4d(&sm_maps.e_row, sm + k1b::STG_ROW_E, 0, px, 0, pl);
-                            ptx::tma_store_4d(&sm_maps.v_row, sm + k1b::STG_ROW_V, 0, px, 0, pl);
-                            if (left) {
-                                ptx::tma_store_4d(&sm_maps.e_row, sm + k1b::STG_ROW_E, 0, hx, 0, pl);
-                                ptx::tma_store_4d(&sm_maps.v_row, sm + k1b::STG_ROW_V, 0, hx, 0, pl);
-                            }
-                            if (right) {
-                                ptx::tma_store_4d(&sm_maps.e_cor, sm + k1b::STG_COR_E, 0, 0, 0, pl);
-                                ptx::tma_store_4d(&sm_maps.v_cor, sm + k1b::STG_COR_V, 0, 0, 0, pl);
-                            }
-                        }
-                    }
-                    ptx::bulk_commit();
-                }
+                ptx::mbar_arrive(stg_full);                       // the store warp takes it from here
             }
         }
-        if (et == 0) ptx::bulk_wait0();
     }
     ptx::tc_fence_before();
     __syncthreads();
