@@ -125,6 +125,8 @@ int channel_sums(slime_ca* h, int mode, cudaStream_t st) {
     const size_t cells = (size_t)h->g.H * h->g.W;
     const int chunks = (int)((cells + 255) / 256);
     dim3 grid(chunks, h->g.B);
+    // a fresh state also starts the reduction's tickets afresh (they are only non-zero if a launch before was cut short)
+    CK(h, cudaMemsetAsync(h->tickets, 0, (size_t)h->g.B * sizeof(int), st));
     if (is_bf16(h)) k_channel_partials<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)h->X, h->partial, h->g);
     else k_channel_partials<float><<<grid, 256, 0, st>>>((const float*)h->X, h->partial, h->g);
     LAUNCHED(h);
